@@ -1,0 +1,43 @@
+// Internal launch interface between the C-ABI entry points and the kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace h3b {
+
+// Address of this device's status word (0 = ok; see DeviceStatus in sm100_ptx.cuh).
+cudaError_t device_status_word(int **word);
+
+// tcgen05 kernels (attn_tc5.cu). Token-major [B][L][H][128] bf16.
+cudaError_t attn_dense_tc5(void *out, const void *q, const void *k, const void *v, float *lse,
+                           unsigned batch, unsigned lq, unsigned lk, unsigned heads,
+                           unsigned kv_heads, float scale, cudaStream_t stream);
+// Head-major tiled [H][tiles*64][128] bf16 with per-(head, query tile) KV tile lists.
+cudaError_t attn_sparse_tc5(void *out, const void *q, const void *k, const void *v, float *lse,
+                            const int *indices, const int *counts, const int *sizes,
+                            unsigned tiles, unsigned heads, cudaStream_t stream);
+
+// Warp-level mma.sync kernel (attn_mma.cu): causal / GQA bf16 D=128 and fp16 D=64.
+// elem: 0 = bf16 (dim 128), 1 = fp16 (dim 64).
+cudaError_t attn_mma(void *out, const void *q, const void *k, const void *v, float *lse,
+                     unsigned batch, unsigned lq, unsigned lk, unsigned heads, unsigned kv_heads,
+                     float scale, bool causal, int elem, cudaStream_t stream);
+
+// VSA coarse stage and merge (vsa_coarse.cu). `count` of the three tensors are pooled in
+// one launch; scores / compression may be NULL (then not written / not computed).
+cudaError_t vsa_tile_pool3(const void *const src[3], void *const tiled[3], float *const pooled[3],
+                           const int *map, const int *sizes, int tiles, int heads, int count,
+                           cudaStream_t stream);
+cudaError_t vsa_score_select_compress(const float *poolq, const float *poolk, const float *poolv,
+                                      float *scores, int *indices, int *counts,
+                                      float *compression, int tiles, int prefix, int keep,
+                                      int heads, float scale, cudaStream_t stream);
+cudaError_t vsa_untile_merge(void *output, const void *tiled, const void *gate,
+                             const float *compression, const int *map, int tiles, int heads,
+                             cudaStream_t stream);
+
+// Ulysses local transposes (ulysses.cu): out[b][a][c] = in[a][b][c], c in 16-byte units.
+cudaError_t swap_leading_16b(void *out, const void *in, unsigned a, unsigned b, size_t c_units,
+                             cudaStream_t stream);
+
+}  // namespace h3b

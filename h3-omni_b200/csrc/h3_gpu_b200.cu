@@ -1,0 +1,692 @@
+// Host side of the library: the five kernel-adapter entry points, and the attention subset of
+// the reference's GPU primitive ABI (context, tensors, dense / rectangular / sparse attention,
+// Ulysses exchanges) written against them. Argument checks, error strings and return
+// conventions follow the reference's CUDA backend (cuda/h3_gpu_cuda.cu, cuda/vsa.cuh,
+// cuda/parallel.cuh) so a caller cannot tell the two apart on this path.
+#include <nccl.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "../../include/h3b200_attn.h"
+#include "attn_kernels.h"
+
+namespace h3b {
+// One status word per device, written by kernels whose bounded waits or bounds checks fail.
+__device__ int g_device_status = 0;
+
+cudaError_t device_status_word(int **word) {
+    static thread_local int cached_device = -1;
+    static thread_local int *cached = nullptr;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device != cached_device) {
+        e = cudaGetSymbolAddress(reinterpret_cast<void **>(&cached), g_device_status);
+        if (e != cudaSuccess) return e;
+        cached_device = device;
+    }
+    *word = cached;
+    return cudaSuccess;
+}
+}  // namespace h3b
+
+// ======================= 1. kernel-adapter entry points =======================
+
+extern "C" cudaError_t h3_flash_bf16(void *output, const void *query, const void *key,
+                                     const void *value, float *logsumexp, unsigned batch,
+                                     unsigned sequence, unsigned heads, unsigned kv_heads,
+                                     float scale, bool causal, cudaStream_t stream) {
+    if (!output || !query || !key || !value) return cudaErrorInvalidValue;
+    if (!causal)
+        return h3b::attn_dense_tc5(output, query, key, value, logsumexp, batch, sequence, sequence,
+                                   heads, kv_heads, scale, stream);
+    return h3b::attn_mma(output, query, key, value, logsumexp, batch, sequence, sequence, heads,
+                         kv_heads, scale, true, 0, stream);
+}
+
+extern "C" cudaError_t h3_flash3_bf16(void *output, const void *query, const void *key,
+                                      const void *value, float *logsumexp, unsigned batch,
+                                      unsigned sequence, unsigned heads, unsigned kv_heads,
+                                      float scale, cudaStream_t stream) {
+    if (!output || !query || !key || !value) return cudaErrorInvalidValue;
+    return h3b::attn_dense_tc5(output, query, key, value, logsumexp, batch, sequence, sequence,
+                               heads, kv_heads, scale, stream);
+}
+
+extern "C" cudaError_t h3_flash3_f16_d64(void *output, const void *query, const void *key,
+                                         const void *value, float *logsumexp, unsigned batch,
+                                         unsigned sequence, unsigned heads, float scale,
+                                         cudaStream_t stream) {
+    if (!output || !query || !key || !value) return cudaErrorInvalidValue;
+    return h3b::attn_mma(output, query, key, value, logsumexp, batch, sequence, sequence, heads,
+                         heads, scale, false, 1, stream);
+}
+
+extern "C" cudaError_t h3_flash3_cross_bf16(void *output, const void *query, const void *key,
+                                            const void *value, float *logsumexp,
+                                            unsigned query_rows, unsigned key_rows, unsigned heads,
+                                            float scale, cudaStream_t stream) {
+    if (!output || !query || !key || !value) return cudaErrorInvalidValue;
+    return h3b::attn_dense_tc5(output, query, key, value, logsumexp, 1, query_rows, key_rows, heads,
+                               heads, scale, stream);
+}
+
+extern "C" cudaError_t h3_vsa_hopper(void *out, const void *q, const void *k, const void *v,
+                                     float *lse, int *indices, int *counts, int *sizes,
+                                     unsigned tiles, unsigned heads, cudaStream_t stream) {
+    if (!out || !q || !k || !v || !indices || !counts || !sizes) return cudaErrorInvalidValue;
+    if (!tiles || !heads) return cudaErrorNotSupported;  // as cuda/vsa_hopper.cu:13
+    return h3b::attn_sparse_tc5(out, q, k, v, lse, indices, counts, sizes, tiles, heads, stream);
+}
+
+extern "C" cudaError_t h3b_device_status(int *status, int reset) {
+    if (!status) return cudaErrorInvalidValue;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    e = cudaMemcpyFromSymbol(status, h3b::g_device_status, sizeof(int));
+    if (e != cudaSuccess || !reset) return e;
+    const int zero = 0;
+    return cudaMemcpyToSymbol(h3b::g_device_status, &zero, sizeof(int));
+}
+
+// ======================= 2. context and tensors =======================
+
+struct h3_gpu {
+    int device{};
+    cudaStream_t own_stream{}, stream{};
+    char error[512]{};
+};
+struct h3_gpu_tensor {
+    void *data{};
+    size_t elements{}, bytes{};
+    h3_gpu_dtype dtype{};
+    h3_gpu *owner{};
+    bool owns{};
+};
+
+static void set_error(h3_gpu *g, const char *format, ...) {
+    if (!g) return;
+    va_list args;
+    va_start(args, format);
+    vsnprintf(g->error, sizeof g->error, format, args);
+    va_end(args);
+}
+static int cuda_ok(h3_gpu *g, cudaError_t e) {
+    if (e == cudaSuccess) return 1;
+    set_error(g, "CUDA: %s", cudaGetErrorString(e));
+    return 0;
+}
+static size_t dtype_size(h3_gpu_dtype t) {
+    return t == H3_GPU_F32 || t == H3_GPU_U32 ? 4 : t == H3_GPU_I8 ? 1 : 2;
+}
+static h3_gpu_tensor *allocate(h3_gpu *g, size_t elements, h3_gpu_dtype dtype) {
+    if (!g || !elements) return nullptr;
+    auto *t = new (std::nothrow) h3_gpu_tensor{};
+    if (!t) return nullptr;
+    t->elements = elements;
+    t->bytes = elements * dtype_size(dtype);
+    t->dtype = dtype;
+    t->owner = g;
+    t->owns = true;
+    // Stream-ordered allocation, as the reference's pool (cuda/h3_gpu_cuda.cu:215-249).
+    if (!cuda_ok(g, cudaMallocAsync(&t->data, t->bytes, g->stream))) {
+        delete t;
+        return nullptr;
+    }
+    return t;
+}
+static int require_elements(h3_gpu *g, const h3_gpu_tensor *t, size_t n, const char *what) {
+    if (t && t->owner == g && t->elements >= n) return 1;
+    set_error(g, "invalid tensor: %s (need %zu elements)", what, n);
+    return 0;
+}
+static int require_bf16(h3_gpu *g, const h3_gpu_tensor *t, size_t n, const char *what) {
+    if (!require_elements(g, t, n, what)) return 0;
+    if (t->dtype == H3_GPU_BF16) return 1;
+    set_error(g, "expected BF16: %s", what);
+    return 0;
+}
+
+extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
+    auto fail = [&](const char *what, cudaError_t e) -> h3_gpu * {
+        if (error && error_size) snprintf(error, error_size, "%s: %s", what, cudaGetErrorString(e));
+        return nullptr;
+    };
+    int device = 0, major = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return fail("no CUDA device", e);
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+    if (e != cudaSuccess) return fail("device query", e);
+    if (major != 10) {
+        // No fallback: this library holds sm_100a code only.
+        if (error && error_size)
+            snprintf(error, error_size, "libh3b200_attn needs a B200-class GPU (sm_100), found sm_%d0",
+                     major);
+        return nullptr;
+    }
+    auto *g = new (std::nothrow) h3_gpu{};
+    if (!g) return nullptr;
+    g->device = device;
+    e = cudaStreamCreateWithFlags(&g->own_stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        delete g;
+        return fail("stream", e);
+    }
+    g->stream = g->own_stream;
+    return g;
+}
+extern "C" void h3_gpu_free(h3_gpu *g) {
+    if (!g) return;
+    cudaStreamSynchronize(g->stream);
+    cudaStreamDestroy(g->own_stream);
+    delete g;
+}
+extern "C" int h3b_gpu_set_stream(h3_gpu *g, cudaStream_t stream) {
+    if (!g) return 0;
+    g->stream = stream ? stream : g->own_stream;
+    return 1;
+}
+extern "C" cudaStream_t h3b_gpu_stream(const h3_gpu *g) { return g ? g->stream : nullptr; }
+
+extern "C" h3_gpu_tensor *h3_gpu_tensor_new_f32(h3_gpu *g, size_t n) { return allocate(g, n, H3_GPU_F32); }
+extern "C" h3_gpu_tensor *h3_gpu_tensor_new_bf16(h3_gpu *g, size_t n) { return allocate(g, n, H3_GPU_BF16); }
+extern "C" h3_gpu_tensor *h3b_tensor_new_f16(h3_gpu *g, size_t n) { return allocate(g, n, H3_GPU_F16); }
+static h3_gpu_tensor *from_host(h3_gpu *g, const void *values, size_t n, h3_gpu_dtype dtype) {
+    if (!values) return nullptr;
+    auto *t = allocate(g, n, dtype);
+    if (!t) return nullptr;
+    if (!cuda_ok(g, cudaMemcpyAsync(t->data, values, t->bytes, cudaMemcpyHostToDevice, g->stream)) ||
+        !cuda_ok(g, cudaStreamSynchronize(g->stream))) {
+        h3_gpu_tensor_free(t);
+        return nullptr;
+    }
+    return t;
+}
+extern "C" h3_gpu_tensor *h3_gpu_tensor_from_f32(h3_gpu *g, const float *v, size_t n) {
+    return from_host(g, v, n, H3_GPU_F32);
+}
+extern "C" h3_gpu_tensor *h3_gpu_tensor_from_bf16(h3_gpu *g, const uint16_t *v, size_t n) {
+    return from_host(g, v, n, H3_GPU_BF16);
+}
+extern "C" h3_gpu_tensor *h3_gpu_tensor_from_u32(h3_gpu *g, const uint32_t *v, size_t n) {
+    return from_host(g, v, n, H3_GPU_U32);
+}
+extern "C" h3_gpu_tensor *h3b_tensor_wrap(h3_gpu *g, void *device_pointer, size_t elements,
+                                          h3_gpu_dtype dtype) {
+    if (!g || !device_pointer || !elements) return nullptr;
+    auto *t = new (std::nothrow) h3_gpu_tensor{};
+    if (!t) return nullptr;
+    t->data = device_pointer;
+    t->elements = elements;
+    t->bytes = elements * dtype_size(dtype);
+    t->dtype = dtype;
+    t->owner = g;
+    t->owns = false;
+    return t;
+}
+extern "C" void *h3b_tensor_data(const h3_gpu_tensor *t) { return t ? t->data : nullptr; }
+extern "C" void h3_gpu_tensor_free(h3_gpu_tensor *t) {
+    if (!t) return;
+    if (t->owns && t->data) cudaFreeAsync(t->data, t->owner->stream);
+    delete t;
+}
+extern "C" size_t h3_gpu_tensor_elements(const h3_gpu_tensor *t) { return t ? t->elements : 0; }
+extern "C" h3_gpu_dtype h3_gpu_tensor_dtype(const h3_gpu_tensor *t) { return t ? t->dtype : H3_GPU_F32; }
+
+static int read_back(const h3_gpu_tensor *t, void *values, size_t n, h3_gpu_dtype dtype) {
+    if (!t || !values || t->dtype != dtype || n > t->elements) return 0;
+    h3_gpu *g = t->owner;
+    return cuda_ok(g, cudaMemcpyAsync(values, t->data, n * dtype_size(dtype), cudaMemcpyDeviceToHost,
+                                      g->stream)) &&
+           cuda_ok(g, cudaStreamSynchronize(g->stream));
+}
+extern "C" int h3_gpu_tensor_read_f32(const h3_gpu_tensor *t, float *v, size_t n) {
+    return read_back(t, v, n, H3_GPU_F32);
+}
+extern "C" int h3_gpu_tensor_read_bf16(const h3_gpu_tensor *t, uint16_t *v, size_t n) {
+    return read_back(t, v, n, H3_GPU_BF16);
+}
+static int write_range(h3_gpu_tensor *t, size_t offset, const void *values, size_t n,
+                       h3_gpu_dtype dtype) {
+    if (!t || !values || t->dtype != dtype || offset > t->elements || n > t->elements - offset)
+        return 0;
+    h3_gpu *g = t->owner;
+    const size_t size = dtype_size(dtype);
+    return cuda_ok(g, cudaMemcpyAsync(static_cast<char *>(t->data) + offset * size, values, n * size,
+                                      cudaMemcpyHostToDevice, g->stream)) &&
+           cuda_ok(g, cudaStreamSynchronize(g->stream));
+}
+extern "C" int h3_gpu_tensor_write_f32(h3_gpu_tensor *t, const float *v, size_t n) {
+    return write_range(t, 0, v, n, H3_GPU_F32);
+}
+extern "C" int h3_gpu_tensor_write_bf16(h3_gpu_tensor *t, const uint16_t *v, size_t n) {
+    return write_range(t, 0, v, n, H3_GPU_BF16);
+}
+extern "C" int h3_gpu_tensor_write_bf16_range(h3_gpu_tensor *t, size_t offset, const uint16_t *v,
+                                              size_t n) {
+    return write_range(t, offset, v, n, H3_GPU_BF16);
+}
+extern "C" int h3_gpu_begin(h3_gpu *g) { return g != nullptr; }
+extern "C" int h3_gpu_continue(h3_gpu *g) { return g != nullptr; }
+extern "C" int h3_gpu_submit(h3_gpu *g) {
+    if (!g) return 0;
+    if (!cuda_ok(g, cudaStreamSynchronize(g->stream))) return 0;
+    int status = 0;
+    if (!cuda_ok(g, cudaMemcpyFromSymbol(&status, h3b::g_device_status, sizeof(int)))) return 0;
+    if (status) {
+        set_error(g, status == 1 ? "device-side wait timed out (status 1)"
+                                 : "device-side bounds check failed (status %d)", status);
+        return 0;
+    }
+    return 1;
+}
+extern "C" const char *h3_gpu_error(const h3_gpu *g) { return g ? g->error : "no GPU context"; }
+extern "C" int h3_gpu_zero(h3_gpu *g, h3_gpu_tensor *t) {
+    return t && t->owner == g && cuda_ok(g, cudaMemsetAsync(t->data, 0, t->bytes, g->stream));
+}
+extern "C" int h3_gpu_copy_bf16(h3_gpu *g, h3_gpu_tensor *dst, size_t dst_offset,
+                                const h3_gpu_tensor *src, size_t src_offset, size_t n) {
+    if (!require_bf16(g, dst, dst_offset + n, "copy destination") ||
+        !require_bf16(g, src, src_offset + n, "copy source"))
+        return 0;
+    return cuda_ok(g, cudaMemcpyAsync(static_cast<uint16_t *>(dst->data) + dst_offset,
+                                      static_cast<const uint16_t *>(src->data) + src_offset, n * 2,
+                                      cudaMemcpyDeviceToDevice, g->stream));
+}
+extern "C" int h3_gpu_download(h3_gpu *g, const h3_gpu_tensor *t, size_t offset, void *host,
+                               size_t count) {
+    if (!g || !t || t->owner != g || !host || offset > t->bytes || count > t->bytes - offset) return 0;
+    return cuda_ok(g, cudaMemcpyAsync(host, static_cast<const char *>(t->data) + offset, count,
+                                      cudaMemcpyDeviceToHost, g->stream)) &&
+           cuda_ok(g, cudaStreamSynchronize(g->stream));
+}
+
+// ======================= dense / rectangular attention =======================
+
+// cuda/h3_gpu_cuda.cu:1109-1130. The reference allocates a logsumexp tensor per call and frees
+// it right after the enqueue without ever reading it; the kernels here take NULL instead.
+static int sdpa(h3_gpu *g, h3_gpu_tensor *y, const h3_gpu_tensor *q, const h3_gpu_tensor *k,
+                const h3_gpu_tensor *v, unsigned batch, unsigned n, unsigned h, unsigned kh,
+                unsigned d, float scale, bool causal, bool allow_flash3) {
+    if (!g) return 0;
+    if (!n || !h || !kh || h % kh || !d || !batch) return 0;
+    if (d != 128) {
+        set_error(g, "BF16 attention supports head dimension 128 only");
+        return 0;
+    }
+    const size_t qn = (size_t)batch * n * h * d, kn = (size_t)batch * n * kh * d;
+    if (!require_bf16(g, q, qn, "attention query") || !require_bf16(g, k, kn, "attention key") ||
+        !require_bf16(g, v, kn, "attention value") || !require_bf16(g, y, qn, "attention output"))
+        return 0;
+    return cuda_ok(g, !causal && allow_flash3
+                          ? h3_flash3_bf16(y->data, q->data, k->data, v->data, nullptr, batch, n, h,
+                                           kh, scale, g->stream)
+                          : h3_flash_bf16(y->data, q->data, k->data, v->data, nullptr, batch, n, h,
+                                          kh, scale, causal, g->stream));
+}
+extern "C" int h3_gpu_sdpa_bf16(h3_gpu *g, h3_gpu_tensor *y, const h3_gpu_tensor *q,
+                                const h3_gpu_tensor *k, const h3_gpu_tensor *v, uint32_t n,
+                                uint32_t h, uint32_t d, float s) {
+    return sdpa(g, y, q, k, v, 1, n, h, h, d, s, false, true);
+}
+extern "C" int h3_gpu_sdpa_fa2_bf16(h3_gpu *g, h3_gpu_tensor *y, const h3_gpu_tensor *q,
+                                    const h3_gpu_tensor *k, const h3_gpu_tensor *v, uint32_t n,
+                                    uint32_t h, uint32_t d, float s) {
+    return sdpa(g, y, q, k, v, 1, n, h, h, d, s, false, false);
+}
+extern "C" int h3_gpu_gqa_causal_bf16(h3_gpu *g, h3_gpu_tensor *y, const h3_gpu_tensor *q,
+                                      const h3_gpu_tensor *k, const h3_gpu_tensor *v, uint32_t n,
+                                      uint32_t h, uint32_t kh, uint32_t d, float s) {
+    return sdpa(g, y, q, k, v, 1, n, h, kh, d, s, true, true);
+}
+extern "C" int h3_gpu_sdpa_f16_d64(h3_gpu *g, h3_gpu_tensor *y, const h3_gpu_tensor *q,
+                                   const h3_gpu_tensor *k, const h3_gpu_tensor *v, uint32_t n,
+                                   uint32_t h, uint32_t d, float s) {
+    if (!g) return 0;
+    const size_t count = (size_t)n * h * d;
+    if (d != 64 || !n || !h) {
+        set_error(g, "FP16 attention supports head dimension 64 only");
+        return 0;
+    }
+    const h3_gpu_tensor *all[] = {q, k, v, y};
+    const char *names[] = {"FP16 attention query", "FP16 attention key", "FP16 attention value",
+                           "FP16 attention output"};
+    for (int i = 0; i < 4; i++) {
+        if (!require_elements(g, all[i], count, names[i])) return 0;
+        if (all[i]->dtype != H3_GPU_F16) {
+            set_error(g, "expected FP16: %s", names[i]);
+            return 0;
+        }
+    }
+    return cuda_ok(g, h3_flash3_f16_d64(y->data, q->data, k->data, v->data, nullptr, 1, n, h, s,
+                                        g->stream));
+}
+extern "C" int h3_gpu_cross_attention_bf16(h3_gpu *g, h3_gpu_tensor *y, size_t yo,
+                                           const h3_gpu_tensor *q, size_t qo,
+                                           const h3_gpu_tensor *k, const h3_gpu_tensor *v, size_t ko,
+                                           uint32_t nq, uint32_t nk, uint32_t heads) {
+    if (!g) return 0;
+    const size_t width = (size_t)heads * 128;
+    if (!nq || !nk || !heads || !require_elements(g, y, (yo + nq) * width, "live output") ||
+        !require_elements(g, q, (qo + nq) * width, "live query") ||
+        !require_elements(g, k, (ko + nk) * width, "live key") ||
+        !require_elements(g, v, (ko + nk) * width, "live value"))
+        return 0;
+    for (auto *t : {static_cast<const h3_gpu_tensor *>(y), q, k, v})
+        if (t->dtype != H3_GPU_BF16) {
+            set_error(g, "live attention requires BF16");
+            return 0;
+        }
+    return cuda_ok(g, h3_flash3_cross_bf16(static_cast<uint16_t *>(y->data) + yo * width,
+                                           static_cast<const uint16_t *>(q->data) + qo * width,
+                                           static_cast<const uint16_t *>(k->data) + ko * width,
+                                           static_cast<const uint16_t *>(v->data) + ko * width,
+                                           nullptr, nq, nk, heads, 1.0f / sqrtf(128.0f), g->stream));
+}
+
+// ======================= video sparse attention =======================
+
+struct h3_gpu_vsa {
+    h3_gpu *gpu{};
+    int rows{}, heads{}, tiles{}, prefix{}, keep{};
+    bool trace_scores{};
+    h3_gpu_tensor *map{}, *sizes{}, *q{}, *k{}, *v{}, *out{};
+    h3_gpu_tensor *poolq{}, *poolk{}, *poolv{}, *scores{}, *compression{}, *indices{}, *counts{};
+};
+
+extern "C" void h3_gpu_vsa_free(h3_gpu_vsa *s) {
+    if (!s) return;
+    for (auto *t : {s->map, s->sizes, s->q, s->k, s->v, s->out, s->poolq, s->poolk, s->poolv,
+                    s->scores, s->compression, s->indices, s->counts})
+        h3_gpu_tensor_free(t);
+    delete s;
+}
+
+// Tile map of cuda/vsa.cuh:192-242: dense 64-row text and audio tiles, then 4x4x4 cubes of the
+// (time, height, width) token grid in raster order with (dt, dy, dx) order inside a cube.
+extern "C" h3_gpu_vsa *h3_gpu_vsa_new(h3_gpu *g, uint32_t text, uint32_t audio, uint32_t time,
+                                      uint32_t height, uint32_t width, uint32_t heads) {
+    if (!g || !text || !audio || !time || !height || !width || !heads) return nullptr;
+    constexpr uint64_t MAX_TILES = 4096;
+    const uint64_t blocks = ((uint64_t)text + 63) / 64 + ((uint64_t)audio + 63) / 64;
+    const uint64_t nt = ((uint64_t)time + 3) / 4, nh = ((uint64_t)height + 3) / 4,
+                   nw = ((uint64_t)width + 3) / 4;
+    if (blocks >= MAX_TILES || nt > MAX_TILES || nh > MAX_TILES || nw > MAX_TILES ||
+        blocks + nt * nh * nw > MAX_TILES || heads > 56) {
+        set_error(g, "VSA requires at most %d tiles and 56 heads", (int)MAX_TILES);
+        return nullptr;
+    }
+    std::vector<int> map, sizes;
+    try {
+        map.reserve((blocks + nt * nh * nw) * 64);
+        sizes.reserve(blocks + nt * nh * nw);
+    } catch (const std::bad_alloc &) {
+        set_error(g, "out of host memory constructing VSA tiles");
+        return nullptr;
+    }
+    int cursor = 0, prefix = 0;
+    for (uint32_t count : {text, audio}) {
+        for (uint32_t i = 0; i < count; i += 64, ++prefix) {
+            const int valid = (int)std::min<uint32_t>(64, count - i);
+            sizes.push_back(valid);
+            for (int j = 0; j < 64; j++) map.push_back(j < valid ? cursor + (int)i + j : -1);
+        }
+        cursor += (int)count;
+    }
+    for (uint32_t t = 0; t < time; t += 4)
+        for (uint32_t y = 0; y < height; y += 4)
+            for (uint32_t x = 0; x < width; x += 4) {
+                const size_t start = map.size();
+                for (uint32_t dt = t; dt < std::min(time, t + 4); dt++)
+                    for (uint32_t dy = y; dy < std::min(height, y + 4); dy++)
+                        for (uint32_t dx = x; dx < std::min(width, x + 4); dx++)
+                            map.push_back(cursor + (int)((dt * height + dy) * width + dx));
+                sizes.push_back((int)(map.size() - start));
+                map.resize(start + 64, -1);
+            }
+    auto *s = new (std::nothrow) h3_gpu_vsa{};
+    if (!s) return nullptr;
+    s->gpu = g;
+    s->rows = cursor + (int)(time * height * width);
+    s->heads = (int)heads;
+    s->tiles = (int)sizes.size();
+    s->prefix = prefix;
+    s->keep = std::max(1, (s->tiles - prefix + 9) / 10);  // cuda/vsa.cuh:242
+    const size_t n = map.size() * heads * 128, pool = sizes.size() * heads * 128;
+    s->map = allocate(g, map.size(), H3_GPU_U32);
+    s->sizes = allocate(g, sizes.size(), H3_GPU_U32);
+    s->q = allocate(g, n, H3_GPU_BF16);
+    s->k = allocate(g, n, H3_GPU_BF16);
+    s->v = allocate(g, n, H3_GPU_BF16);
+    s->out = allocate(g, n, H3_GPU_BF16);
+    s->poolq = allocate(g, pool, H3_GPU_F32);
+    s->poolk = allocate(g, pool, H3_GPU_F32);
+    s->poolv = allocate(g, pool, H3_GPU_F32);
+    s->compression = allocate(g, pool, H3_GPU_F32);
+    s->indices = allocate(g, sizes.size() * sizes.size() * heads, H3_GPU_U32);
+    s->counts = allocate(g, sizes.size() * heads, H3_GPU_U32);
+    if (!s->map || !s->sizes || !s->q || !s->k || !s->v || !s->out || !s->poolq || !s->poolk ||
+        !s->poolv || !s->compression || !s->indices || !s->counts ||
+        !cuda_ok(g, cudaMemcpyAsync(s->map->data, map.data(), map.size() * sizeof(int),
+                                    cudaMemcpyHostToDevice, g->stream)) ||
+        !cuda_ok(g, cudaMemcpyAsync(s->sizes->data, sizes.data(), sizes.size() * sizeof(int),
+                                    cudaMemcpyHostToDevice, g->stream)) ||
+        !cuda_ok(g, cudaStreamSynchronize(g->stream))) {
+        h3_gpu_vsa_free(s);
+        return nullptr;
+    }
+    return s;
+}
+
+extern "C" int h3b_vsa_info(const h3_gpu_vsa *s, int *rows, int *tiles, int *prefix, int *keep) {
+    if (!s) return 0;
+    if (rows) *rows = s->rows;
+    if (tiles) *tiles = s->tiles;
+    if (prefix) *prefix = s->prefix;
+    if (keep) *keep = s->keep;
+    return 1;
+}
+extern "C" int h3b_vsa_set_keep(h3_gpu_vsa *s, int keep) {
+    if (!s || keep < 1 || keep > s->tiles - s->prefix) return 0;
+    s->keep = keep;
+    return 1;
+}
+extern "C" int h3b_vsa_trace_scores(h3_gpu_vsa *s, int enable) {
+    if (!s) return 0;
+    if (enable && !s->scores) {
+        s->scores = allocate(s->gpu, (size_t)s->tiles * s->tiles * s->heads, H3_GPU_F32);
+        if (!s->scores) return 0;
+    }
+    s->trace_scores = enable != 0;
+    return 1;
+}
+extern "C" void *h3b_vsa_buffer(const h3_gpu_vsa *s, int which) {
+    if (!s) return nullptr;
+    const h3_gpu_tensor *all[] = {s->map, s->sizes, s->q, s->k, s->v, s->out, s->poolq, s->poolk,
+                                  s->poolv, s->indices, s->counts, s->compression, s->scores};
+    if (which < 0 || which >= (int)(sizeof all / sizeof all[0]) || !all[which]) return nullptr;
+    return all[which]->data;
+}
+
+// cuda/vsa.cuh:263-300, as three launches around the block-sparse kernel.
+extern "C" int h3_gpu_vsa_bf16(h3_gpu_vsa *s, h3_gpu_tensor *out, const h3_gpu_tensor *q,
+                               const h3_gpu_tensor *k, const h3_gpu_tensor *value,
+                               const h3_gpu_tensor *gate) {
+    if (!s) return 0;
+    h3_gpu *g = s->gpu;
+    const size_t elements = (size_t)s->rows * s->heads * 128;
+    const h3_gpu_tensor *tensors[] = {out, q, k, value, gate};
+    for (auto *t : tensors)
+        if (!require_bf16(g, t, elements, "VSA input/output")) return 0;
+    const void *src[3] = {q->data, k->data, value->data};
+    void *tiled[3] = {s->q->data, s->k->data, s->v->data};
+    float *pooled[3] = {(float *)s->poolq->data, (float *)s->poolk->data, (float *)s->poolv->data};
+    const int *map = (const int *)s->map->data, *sizes = (const int *)s->sizes->data;
+    if (!cuda_ok(g, h3b::vsa_tile_pool3(src, tiled, pooled, map, sizes, s->tiles, s->heads, 3,
+                                        g->stream)))
+        return 0;
+    const float scale = 1.0f / sqrtf(128.0f);
+    if (!cuda_ok(g, h3b::vsa_score_select_compress(
+                        pooled[0], pooled[1], pooled[2],
+                        s->trace_scores ? (float *)s->scores->data : nullptr,
+                        (int *)s->indices->data, (int *)s->counts->data,
+                        (float *)s->compression->data, s->tiles, s->prefix, s->keep, s->heads, scale,
+                        g->stream)))
+        return 0;
+    if (!cuda_ok(g, h3_vsa_hopper(s->out->data, s->q->data, s->k->data, s->v->data, nullptr,
+                                  (int *)s->indices->data, (int *)s->counts->data,
+                                  (int *)s->sizes->data, s->tiles, s->heads, g->stream)))
+        return 0;
+    return cuda_ok(g, h3b::vsa_untile_merge(out->data, s->out->data, gate->data,
+                                            (const float *)s->compression->data, map, s->tiles,
+                                            s->heads, g->stream));
+}
+
+// ======================= multi-GPU: communicators and Ulysses =======================
+
+struct h3_gpu_comm {
+    ncclComm_t comm;
+    int rank;
+    int size;
+};
+static int nccl_ok(h3_gpu *g, ncclResult_t r, const char *what) {
+    if (r == ncclSuccess) return 1;
+    set_error(g, "NCCL %s: %s", what, ncclGetErrorString(r));
+    return 0;
+}
+extern "C" int h3_gpu_device_count(void) {
+    int count = 0;
+    return cudaGetDeviceCount(&count) == cudaSuccess ? count : 0;
+}
+extern "C" int h3_gpu_select_device(int device, char *error, size_t size) {
+    cudaError_t e = cudaSetDevice(device);
+    if (e == cudaSuccess) return 1;
+    if (error && size)
+        snprintf(error, size, "cannot select CUDA device %d: %s", device, cudaGetErrorString(e));
+    return 0;
+}
+extern "C" int h3_gpu_comm_init_all(int count, h3_gpu_comm **comms, char *error, size_t size) {
+    if (count < 1 || count > 64 || !comms) {
+        if (error && size) snprintf(error, size, "invalid NCCL communicator count %d", count);
+        return 0;
+    }
+    std::vector<ncclComm_t> raw(count);
+    std::vector<int> devices(count);
+    for (int i = 0; i < count; i++) devices[i] = i;
+    ncclResult_t r = ncclCommInitAll(raw.data(), count, devices.data());
+    if (r != ncclSuccess) {
+        if (error && size) snprintf(error, size, "NCCL init: %s", ncclGetErrorString(r));
+        return 0;
+    }
+    for (int i = 0; i < count; i++) comms[i] = new h3_gpu_comm{raw[i], i, count};
+    return 1;
+}
+extern "C" int h3b_comm_unique_id(void *id128, char *error, size_t size) {
+    static_assert(sizeof(ncclUniqueId) == 128, "unique id size");
+    ncclUniqueId id;
+    ncclResult_t r = id128 ? ncclGetUniqueId(&id) : ncclInvalidArgument;
+    if (r != ncclSuccess) {
+        if (error && size) snprintf(error, size, "NCCL unique id: %s", ncclGetErrorString(r));
+        return 0;
+    }
+    memcpy(id128, &id, sizeof id);
+    return 1;
+}
+extern "C" int h3b_comm_init_rank(const void *id128, int rank, int count, h3_gpu_comm **comm,
+                                  char *error, size_t size) {
+    if (!id128 || !comm || count < 1 || rank < 0 || rank >= count) {
+        if (error && size) snprintf(error, size, "invalid NCCL rank %d of %d", rank, count);
+        return 0;
+    }
+    ncclUniqueId id;
+    memcpy(&id, id128, sizeof id);
+    ncclComm_t raw;
+    ncclResult_t r = ncclCommInitRank(&raw, count, id, rank);
+    if (r != ncclSuccess) {
+        if (error && size) snprintf(error, size, "NCCL init: %s", ncclGetErrorString(r));
+        return 0;
+    }
+    *comm = new h3_gpu_comm{raw, rank, count};
+    return 1;
+}
+extern "C" int h3b_comm_rank(const h3_gpu_comm *c) { return c ? c->rank : -1; }
+extern "C" int h3b_comm_size(const h3_gpu_comm *c) { return c ? c->size : 0; }
+extern "C" void h3_gpu_comm_free(h3_gpu_comm *c) {
+    if (!c) return;
+    if (c->comm) ncclCommDestroy(c->comm);
+    delete c;
+}
+// Unblocks every rank waiting in a collective after one rank failed (cuda/parallel.cuh:60-65).
+extern "C" void h3_gpu_comm_abort(h3_gpu_comm *c) {
+    if (c && c->comm) ncclCommAbort(c->comm);
+    if (c) c->comm = nullptr;
+}
+
+static int swap_leading_bf16(h3_gpu *g, void *out, const void *in, unsigned a, unsigned b,
+                             size_t c_elements) {
+    const size_t bytes = c_elements * 2;
+    if (bytes % 16) {
+        set_error(g, "Ulysses block of %zu bytes is not 16-byte aligned", bytes);
+        return 0;
+    }
+    return cuda_ok(g, h3b::swap_leading_16b(out, in, a, b, bytes / 16, g->stream));
+}
+// Every rank sends block j of `send` to rank j and receives rank j's block into block j.
+static int all_to_all(h3_gpu *g, h3_gpu_comm *c, void *recv, const void *send, size_t block_bytes) {
+    if (!nccl_ok(g, ncclGroupStart(), "group start")) return 0;
+    for (int peer = 0; peer < c->size; peer++) {
+        ncclResult_t r = ncclSend((const char *)send + peer * block_bytes, block_bytes, ncclUint8,
+                                  peer, c->comm, g->stream);
+        if (r == ncclSuccess)
+            r = ncclRecv((char *)recv + peer * block_bytes, block_bytes, ncclUint8, peer, c->comm,
+                         g->stream);
+        if (r != ncclSuccess) {
+            ncclGroupEnd();
+            return nccl_ok(g, r, "all-to-all");
+        }
+    }
+    return nccl_ok(g, ncclGroupEnd(), "group end");
+}
+static int ulysses_check(h3_gpu *g, h3_gpu_comm *c, const h3_gpu_tensor *t,
+                         const h3_gpu_tensor *scratch, unsigned rows, unsigned heads, unsigned dim) {
+    const size_t count = (size_t)rows * heads * dim;
+    if (!c || !c->comm || heads % c->size) {
+        set_error(g, "Ulysses: %u heads do not split over %d ranks", heads, c ? c->size : 0);
+        return 0;
+    }
+    return require_bf16(g, t, count, "Ulysses tensor") &&
+           require_bf16(g, scratch, count, "Ulysses scratch");
+}
+// [rows][heads][dim] on each rank -> [ranks*rows][heads/ranks][dim] (cuda/parallel.cuh:125-133).
+extern "C" int h3_gpu_ulysses_scatter_heads_bf16(h3_gpu *g, h3_gpu_comm *c, h3_gpu_tensor *t,
+                                                 h3_gpu_tensor *scratch, uint32_t rows,
+                                                 uint32_t heads, uint32_t dim) {
+    if (!g || !ulysses_check(g, c, t, scratch, rows, heads, dim)) return 0;
+    const size_t group = (size_t)(heads / c->size) * dim;
+    return swap_leading_bf16(g, scratch->data, t->data, rows, c->size, group) &&
+           all_to_all(g, c, t->data, scratch->data, (size_t)rows * group * 2);
+}
+// The inverse (cuda/parallel.cuh:135-143).
+extern "C" int h3_gpu_ulysses_gather_heads_bf16(h3_gpu *g, h3_gpu_comm *c, h3_gpu_tensor *t,
+                                                h3_gpu_tensor *scratch, uint32_t rows,
+                                                uint32_t heads, uint32_t dim) {
+    if (!g || !ulysses_check(g, c, t, scratch, rows, heads, dim)) return 0;
+    const size_t group = (size_t)(heads / c->size) * dim;
+    return all_to_all(g, c, scratch->data, t->data, (size_t)rows * group * 2) &&
+           swap_leading_bf16(g, t->data, scratch->data, c->size, rows, group);
+}
+// output[rank * count + i] = input_of_rank[i] (cuda/parallel.cuh:146-153).
+extern "C" int h3_gpu_all_gather_bf16(h3_gpu *g, h3_gpu_comm *c, h3_gpu_tensor *output,
+                                      const h3_gpu_tensor *input, size_t count) {
+    if (!g || !c || !c->comm || !require_bf16(g, input, count, "all-gather input") ||
+        !require_bf16(g, output, count * c->size, "all-gather output"))
+        return 0;
+    return nccl_ok(g, ncclAllGather(input->data, output->data, count * 2, ncclUint8, c->comm,
+                                    g->stream), "all-gather");
+}

@@ -1,0 +1,386 @@
+// Video sparse attention, coarse stage and merge: token-cube pooling, pooled scores with
+// warp-level top-k tile selection, the pooled-softmax compression branch, and the gated
+// merge back to token-major rows. These are HBM-bound passes; they replace tile_pool,
+// the two cuBLAS SGEMMs, select_blocks, pooled_softmax and untile_merge of the reference's
+// cuda/vsa.cuh:18-181,263-300 with three launches (pool x3 fused, score+select+compress,
+// merge) and never materialise the [heads][tiles][tiles] score matrix unless asked to.
+#include <cuda_bf16.h>
+#include <math_constants.h>
+
+#include "attn_kernels.h"
+
+namespace h3b {
+namespace {
+
+constexpr int VD = 128, VT = 64;
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t x) { return __uint_as_float(x << 16); }
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float x) {
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x));
+}
+__device__ __forceinline__ float bf16_round(float x) { return bf16_bits_to_f32(f32_to_bf16_bits(x)); }
+
+// ---- pooling ---------------------------------------------------------------------
+// One CTA = one tile x 4 heads x one of {Q, K, V}; thread = (head, pair of dims), so every
+// token row contributes one contiguous 1 KB read per CTA. The per-dimension summation order
+// is the reference's (cuda/vsa.cuh:22-42): 4 lanes x 4 slot accumulators, element
+// i = lane + 4*slot + 16*round, ((a0+a1)+a2)+a3 per lane, (l0+l2)+(l1+l3), then / size.
+struct PoolArgs {
+    const uint32_t *src[3];
+    uint32_t *tiled[3];
+    float *pooled[3];
+};
+
+__global__ void __launch_bounds__(256)
+tile_pool_kernel(PoolArgs a, const int *__restrict__ map, const int *__restrict__ sizes, int tiles,
+                 int heads) {
+    __shared__ int rows[VT];
+    const int tile = blockIdx.x, which = blockIdx.z;
+    const int head = blockIdx.y * 4 + (threadIdx.x >> 6), dp = threadIdx.x & 63;
+    if (threadIdx.x < VT) rows[threadIdx.x] = map[tile * VT + threadIdx.x];
+    __syncthreads();
+    if (head >= heads) return;
+    const uint32_t *src = a.src[which];
+    uint32_t *tiled = a.tiled[which];
+    float lane_lo[4], lane_hi[4];
+#pragma unroll
+    for (int lane = 0; lane < 4; lane++) {
+        float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int round = 0; round < 4; round++) {
+#pragma unroll
+            for (int slot = 0; slot < 4; slot++) {
+                const int i = lane + slot * 4 + round * 16;
+                const int row = rows[i];
+                const uint32_t x =
+                    row < 0 ? 0u : __ldg(src + ((size_t)row * heads + head) * (VD / 2) + dp);
+                if (tiled)
+                    tiled[((size_t)head * tiles * VT + tile * VT + i) * (VD / 2) + dp] = x;
+                lo[slot] += bf16_bits_to_f32(x & 0xffffu);
+                hi[slot] += bf16_bits_to_f32(x >> 16);
+            }
+        }
+        lane_lo[lane] = ((lo[0] + lo[1]) + lo[2]) + lo[3];
+        lane_hi[lane] = ((hi[0] + hi[1]) + hi[2]) + hi[3];
+    }
+    const float size = (float)sizes[tile];
+    float2 mean;
+    mean.x = ((lane_lo[0] + lane_lo[2]) + (lane_lo[1] + lane_lo[3])) / size;
+    mean.y = ((lane_hi[0] + lane_hi[2]) + (lane_hi[1] + lane_hi[3])) / size;
+    reinterpret_cast<float2 *>(a.pooled[which])[((size_t)head * tiles + tile) * (VD / 2) + dp] = mean;
+}
+
+// ---- scores + top-k selection + compression -----------------------------------------
+constexpr int QT = 8;        // query tiles per CTA, one warp each for selection/softmax
+constexpr int CHUNK = 32;    // pooled K/V rows staged per step
+constexpr int PADDED = VD + 1;
+
+// Order-preserving key of a float, the one cub's radix sort uses: larger float -> larger key.
+__device__ __forceinline__ uint32_t sort_key(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// scores row = scale * fmaf-chain over d = 0..127 (ascending), one fixed order.
+// Selection (cuda/vsa.cuh:47-76): prefix query tiles keep all tiles; video query tiles keep
+// all prefix tiles plus the `keep` best video tiles (ties: lower index first), ascending.
+// Compression (cuda/vsa.cuh:80-166,291-294): softmax over the whole row in the ATen lane
+// order, then sum_k p[k] * poolv[k][:] as one fmaf chain over k ascending.
+__global__ void __launch_bounds__(256)
+score_select_kernel(const float *__restrict__ poolq, const float *__restrict__ poolk,
+                    const float *__restrict__ poolv, float *__restrict__ scores_out,
+                    int *__restrict__ indices, int *__restrict__ counts,
+                    float *__restrict__ compression, int tiles, int prefix, int keep, float scale) {
+    extern __shared__ float sm[];
+    float *row_scores = sm;                               // [QT][tiles]
+    float *stage = row_scores + (size_t)QT * tiles;       // [CHUNK][PADDED]
+    float *qrows = stage + CHUNK * PADDED;                // [QT][VD]
+    int *hist = reinterpret_cast<int *>(qrows + QT * VD); // [QT][256]
+
+    const int head = blockIdx.y, qt0 = blockIdx.x * QT;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nq = min(QT, tiles - qt0);
+    const float *pk = poolk + (size_t)head * tiles * VD;
+
+    for (int i = tid; i < QT * VD; i += 256) {
+        const int qi = i / VD;
+        qrows[i] = qi < nq ? poolq[((size_t)head * tiles + qt0 + qi) * VD + (i % VD)] : 0.0f;
+    }
+    // Scores: stage CHUNK key rows, then thread (kt_local, query group) does its dot products.
+    for (int k0 = 0; k0 < tiles; k0 += CHUNK) {
+        __syncthreads();
+        for (int i = tid; i < CHUNK * VD; i += 256) {
+            const int r = i / VD, d = i % VD;
+            stage[r * PADDED + d] = k0 + r < tiles ? pk[(size_t)(k0 + r) * VD + d] : 0.0f;
+        }
+        __syncthreads();
+        const int r = tid & 31, qi = tid >> 5;  // 32 key rows x 8 query tiles
+        if (k0 + r < tiles && qi < nq) {
+            float dot = 0.0f;
+            const float *kr = stage + r * PADDED, *qr = qrows + qi * VD;
+#pragma unroll 16
+            for (int d = 0; d < VD; d++) dot = fmaf(qr[d], kr[d], dot);
+            row_scores[(size_t)qi * tiles + k0 + r] = scale * dot;
+        }
+    }
+    __syncthreads();
+
+    // ---- selection: warp `warp` owns query tile qt0 + warp ----
+    const int qt = qt0 + warp;
+    float *mine = row_scores + (size_t)warp * tiles;
+    if (warp < nq) {
+        const size_t row = (size_t)head * tiles + qt;
+        if (scores_out)
+            for (int j = lane; j < tiles; j += 32) scores_out[row * tiles + j] = mine[j];
+        int *dst = indices + row * tiles;
+        if (qt < prefix) {
+            for (int j = lane; j < tiles; j += 32) dst[j] = j;
+            if (lane == 0) counts[row] = tiles;
+        } else {
+            // Radix select of the keep-th largest key among video tiles, 8 bits per pass.
+            int *h = hist + warp * 256;
+            uint32_t want = 0u, mask = 0u;
+            int remaining = keep;
+            for (int pass = 3; pass >= 0; pass--) {
+                for (int b = lane; b < 256; b += 32) h[b] = 0;
+                __syncwarp();
+                for (int j = prefix + lane; j < tiles; j += 32) {
+                    const uint32_t key = sort_key(mine[j]);
+                    if ((key & mask) == want) atomicAdd(&h[(key >> (8 * pass)) & 255u], 1);
+                }
+                __syncwarp();
+                // lane L owns bins 255-8L .. 248-8L, highest first
+                int local[8], sum = 0;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    local[i] = h[255 - 8 * lane - i];
+                    sum += local[i];
+                }
+                int before = sum;  // inclusive scan over lanes, then make it exclusive
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, before, o);
+                    if (lane >= o) before += up;
+                }
+                before -= sum;
+                const bool owner = before < remaining && remaining <= before + sum;
+                int bin = 0, above = 0;
+                if (owner) {
+                    int acc = before;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        if (acc < remaining && remaining <= acc + local[i]) {
+                            bin = 255 - 8 * lane - i;
+                            above = acc;
+                        }
+                        acc += local[i];
+                    }
+                }
+                const unsigned who = __ballot_sync(0xffffffffu, owner);
+                const int src = who ? __ffs(who) - 1 : 0;
+                bin = __shfl_sync(0xffffffffu, bin, src);
+                above = __shfl_sync(0xffffffffu, above, src);
+                remaining -= above;
+                want |= (uint32_t)bin << (8 * pass);
+                mask |= 0xffu << (8 * pass);
+                __syncwarp();
+            }
+            // `want` is the threshold key; take every larger key and the first `remaining`
+            // equal keys in index order; emit ascending.
+            int written = 0, equal_seen = 0;
+            for (int base = 0; base < tiles; base += 32) {
+                const int j = base + lane;
+                bool take = false, equal = false;
+                if (j < tiles) {
+                    if (j < prefix) {
+                        take = true;
+                    } else {
+                        const uint32_t key = sort_key(mine[j]);
+                        take = key > want;
+                        equal = key == want;
+                    }
+                }
+                const unsigned eq_mask = __ballot_sync(0xffffffffu, equal);
+                if (equal && equal_seen + __popc(eq_mask & ((1u << lane) - 1u)) < remaining)
+                    take = true;
+                equal_seen += __popc(eq_mask);
+                const unsigned take_mask = __ballot_sync(0xffffffffu, take);
+                if (take) dst[written + __popc(take_mask & ((1u << lane) - 1u))] = j;
+                written += __popc(take_mask);
+            }
+            if (lane == 0) counts[row] = written;
+        }
+    }
+
+    // ---- pooled softmax (in place, ATen reduction order) ----
+    if (compression && warp < nq) {
+        float largest = -CUDART_INF_F, total = 0.0f;
+        if (tiles <= 2048) {
+            for (int j = lane; j < tiles; j += 32) largest = fmaxf(largest, mine[j]);
+#pragma unroll
+            for (int o = 16; o; o >>= 1)
+                largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, o));
+            for (int j = lane; j < tiles; j += 32) {
+                const float e = expf(mine[j] - largest);
+                mine[j] = e;
+                total += e;
+            }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        } else {
+            // 1024-thread two-level shuffle-down order of the reference's block variant:
+            // virtual thread t = w*32 + lane sums columns t, t+1024, ...
+            for (int j = lane; j < tiles; j += 32) largest = fmaxf(largest, mine[j]);
+#pragma unroll
+            for (int o = 16; o; o >>= 1)
+                largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, o));
+            float warp_sums = 0.0f;  // lane w keeps virtual warp w's sum
+            for (int w = 0; w < 32; w++) {
+                float part = 0.0f;
+                for (int i = 0; i < 4; i++) {
+                    const int col = w * 32 + lane + i * 1024;
+                    if (col < tiles) part += expf(mine[col] - largest);
+                }
+#pragma unroll
+                for (int o = 16; o; o >>= 1) {
+                    const float other = __shfl_down_sync(0xffffffffu, part, o);
+                    part += other;
+                }
+                part = __shfl_sync(0xffffffffu, part, 0);
+                if (lane == w) warp_sums = part;
+            }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) {
+                const float other = __shfl_down_sync(0xffffffffu, warp_sums, o);
+                warp_sums += other;
+            }
+            total = __shfl_sync(0xffffffffu, warp_sums, 0);
+            for (int j = lane; j < tiles; j += 32) mine[j] = expf(mine[j] - largest);
+        }
+        __syncwarp();
+        for (int j = lane; j < tiles; j += 32) mine[j] = mine[j] / total;
+    }
+    if (!compression) return;
+
+    // ---- compression: lane owns dims 4*lane..4*lane+3 of its warp's query tile ----
+    const float *pv = poolv + (size_t)head * tiles * VD;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 *stage4 = reinterpret_cast<float4 *>(stage);  // [CHUNK][VD/4], unpadded reuse
+    for (int k0 = 0; k0 < tiles; k0 += CHUNK) {
+        __syncthreads();
+        for (int i = tid; i < CHUNK * (VD / 4); i += 256) {
+            const int r = i / (VD / 4);
+            stage4[i] = k0 + r < tiles
+                            ? reinterpret_cast<const float4 *>(pv + (size_t)(k0 + r) * VD)[i % (VD / 4)]
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        __syncthreads();
+        if (warp < nq) {
+            const int n = min(CHUNK, tiles - k0);
+            for (int r = 0; r < n; r++) {
+                const float pr = mine[k0 + r];
+                const float4 vv = stage4[r * (VD / 4) + lane];
+                acc.x = fmaf(pr, vv.x, acc.x);
+                acc.y = fmaf(pr, vv.y, acc.y);
+                acc.z = fmaf(pr, vv.z, acc.z);
+                acc.w = fmaf(pr, vv.w, acc.w);
+            }
+        }
+    }
+    if (warp < nq)
+        reinterpret_cast<float4 *>(compression + ((size_t)head * tiles + qt) * VD)[lane] = acc;
+}
+
+// ---- merge ---------------------------------------------------------------------------
+// out[row][h][:] = bf16(fmaf(bf16_round(compression[h][tile][:]), gate[row][h][:], sparse))
+// for every non-padded tiled row (cuda/vsa.cuh:168-181); one 16-byte vector per thread.
+__global__ void __launch_bounds__(256)
+untile_merge_kernel(uint4 *__restrict__ output, const uint4 *__restrict__ tiled,
+                    const uint4 *__restrict__ gate, const float *__restrict__ compression,
+                    const int *__restrict__ map, int tiles, int heads) {
+    const size_t total = (size_t)tiles * VT * heads * (VD / 8);
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int v = (int)(i % (VD / 8));
+    const int head = (int)((i / (VD / 8)) % heads);
+    const int padded = (int)(i / ((size_t)(VD / 8) * heads));
+    const int row = map[padded];
+    if (row < 0) return;
+    const uint4 x = tiled[((size_t)head * tiles * VT + padded) * (VD / 8) + v];
+    const size_t dst = ((size_t)row * heads + head) * (VD / 8) + v;
+    const uint4 gt = gate[dst];
+    const float4 *cp = reinterpret_cast<const float4 *>(
+        compression + ((size_t)head * tiles + padded / VT) * VD + v * 8);
+    const float4 c0 = cp[0], c1 = cp[1];
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, gs[4] = {gt.x, gt.y, gt.z, gt.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const float lo = fmaf(bf16_round(c[2 * k]), bf16_bits_to_f32(gs[k] & 0xffffu),
+                              bf16_bits_to_f32(xs[k] & 0xffffu));
+        const float hi = fmaf(bf16_round(c[2 * k + 1]), bf16_bits_to_f32(gs[k] >> 16),
+                              bf16_bits_to_f32(xs[k] >> 16));
+        o[k] = f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
+    }
+    output[dst] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+}  // namespace
+
+cudaError_t vsa_tile_pool3(const void *const src[3], void *const tiled[3], float *const pooled[3],
+                           const int *map, const int *sizes, int tiles, int heads, int count,
+                           cudaStream_t stream) {
+    PoolArgs a{};
+    for (int i = 0; i < count; i++) {
+        a.src[i] = static_cast<const uint32_t *>(src[i]);
+        a.tiled[i] = static_cast<uint32_t *>(tiled[i]);
+        a.pooled[i] = pooled[i];
+    }
+    dim3 grid(tiles, (heads + 3) / 4, count);
+    tile_pool_kernel<<<grid, 256, 0, stream>>>(a, map, sizes, tiles, heads);
+    return cudaGetLastError();
+}
+
+static size_t score_select_smem(int tiles) {
+    return sizeof(float) * ((size_t)QT * tiles + CHUNK * PADDED + QT * VD) + sizeof(int) * QT * 256;
+}
+
+cudaError_t vsa_score_select_compress(const float *poolq, const float *poolk, const float *poolv,
+                                      float *scores, int *indices, int *counts,
+                                      float *compression, int tiles, int prefix, int keep,
+                                      int heads, float scale, cudaStream_t stream) {
+    if (tiles < 1 || tiles > 4096 || keep < 1 || prefix < 0 || prefix > tiles)
+        return cudaErrorInvalidValue;
+    const size_t smem = score_select_smem(tiles);
+    static thread_local size_t configured = 0;
+    static thread_local int configured_device = -1;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (configured_device != device || smem > configured) {
+        e = cudaFuncSetAttribute(score_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)score_select_smem(4096));
+        if (e != cudaSuccess) return e;
+        configured = score_select_smem(4096);
+        configured_device = device;
+    }
+    dim3 grid((tiles + QT - 1) / QT, heads);
+    score_select_kernel<<<grid, 256, smem, stream>>>(poolq, poolk, poolv, scores, indices, counts,
+                                                     compression, tiles, prefix, keep, scale);
+    return cudaGetLastError();
+}
+
+cudaError_t vsa_untile_merge(void *output, const void *tiled, const void *gate,
+                             const float *compression, const int *map, int tiles, int heads,
+                             cudaStream_t stream) {
+    const size_t total = (size_t)tiles * VT * heads * (VD / 8);
+    const size_t blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffu) return cudaErrorInvalidValue;
+    untile_merge_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+        static_cast<uint4 *>(output), static_cast<const uint4 *>(tiled),
+        static_cast<const uint4 *>(gate), compression, map, tiles, heads);
+    return cudaGetLastError();
+}
+
+}  // namespace h3b

@@ -1,0 +1,195 @@
+/*
+ * libh3b200_attn - B200 (sm_100a) attention engine for the H3-omni diffusion transformer.
+ *
+ * C ABI, three layers:
+ *   1. The five kernel-adapter symbols the reference's CUDA backend links against
+ *      (reference cuda/h3_flash.h:4-20 and cuda/vsa_hopper.h:4-6). Exporting these is what
+ *      makes the library a drop-in for the reference's FlashAttention-2/3 and Hopper VSA
+ *      adapter objects.
+ *   2. A mirror of the reference's GPU primitive ABI for the attention path only
+ *      (reference h3_gpu.h and cuda/h3_cuda.h): same names, argument meaning and error
+ *      behaviour (return 1 = ok, 0 = failure with a message from h3_gpu_error()).
+ *   3. Additions of this library (prefix h3b_), none of which the reference has.
+ *
+ * All device work is enqueued asynchronously on the context's stream; nothing here
+ * synchronises the host except h3_gpu_submit, tensor reads and h3b_device_status.
+ * A context and its tensors belong to one host thread and one device.
+ */
+#ifndef H3B200_ATTN_H
+#define H3B200_ATTN_H
+
+#include <cuda_runtime.h>
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------
+ * 1. Kernel-adapter symbols. Tensors are token-major [batch][sequence][heads][dim],
+ *    16-bit elements; logsumexp (may be NULL here; the reference never reads it) is
+ *    [batch][heads][sequence] f32 = max*scale + log(sum). Return a cudaError_t, never exit.
+ * ------------------------------------------------------------------------------------ */
+
+/* Replaces reference cuda/flash_attention.cu:29-67 (FlashAttention-2 adapter): bf16,
+ * head dim 128, optional causal mask, grouped-query when kv_heads < heads. */
+cudaError_t h3_flash_bf16(void *output, const void *query, const void *key, const void *value,
+                          float *logsumexp, unsigned batch, unsigned sequence, unsigned heads,
+                          unsigned kv_heads, float scale, bool causal, cudaStream_t stream);
+/* Replaces reference cuda/flash3_attention.cu:74-79 (FlashAttention-3 adapter): bf16,
+ * head dim 128, non-causal. This is the DiT joint video+audio self-attention. */
+cudaError_t h3_flash3_bf16(void *output, const void *query, const void *key, const void *value,
+                           float *logsumexp, unsigned batch, unsigned sequence, unsigned heads,
+                           unsigned kv_heads, float scale, cudaStream_t stream);
+/* Replaces reference cuda/flash3_attention.cu:81-87: fp16, head dim 64 (video VAE). */
+cudaError_t h3_flash3_f16_d64(void *output, const void *query, const void *key, const void *value,
+                              float *logsumexp, unsigned batch, unsigned sequence, unsigned heads,
+                              float scale, cudaStream_t stream);
+/* Replaces reference cuda/flash3_attention.cu:89-94: rectangular bf16 attention,
+ * query_rows x key_rows, batch 1 (live mode: short query chunk against KV history). */
+cudaError_t h3_flash3_cross_bf16(void *output, const void *query, const void *key,
+                                 const void *value, float *logsumexp, unsigned query_rows,
+                                 unsigned key_rows, unsigned heads, float scale,
+                                 cudaStream_t stream);
+/* Replaces reference cuda/vsa_hopper.cu:6-28: block-sparse attention over 64-row tiles.
+ * out, q, k, v: [heads][tiles*64][128] bf16; lse [heads][tiles*64] f32 (may be NULL);
+ * indices [heads][tiles][tiles] (first counts[h][q] entries valid, ascending),
+ * counts [heads][tiles], sizes [tiles] = valid keys per tile. */
+cudaError_t h3_vsa_hopper(void *out, const void *q, const void *k, const void *v, float *lse,
+                          int *indices, int *counts, int *sizes, unsigned tiles, unsigned heads,
+                          cudaStream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * 2. GPU primitive ABI, attention path only (reference h3_gpu.h / cuda/h3_cuda.h).
+ * ------------------------------------------------------------------------------------ */
+typedef struct h3_gpu h3_gpu;
+typedef struct h3_gpu_tensor h3_gpu_tensor;
+typedef struct h3_gpu_comm h3_gpu_comm;
+typedef struct h3_gpu_vsa h3_gpu_vsa;
+
+typedef enum { /* reference h3_gpu.h:10-16 */
+    H3_GPU_F32 = 0,
+    H3_GPU_BF16,
+    H3_GPU_I8,
+    H3_GPU_U32,
+    H3_GPU_F16
+} h3_gpu_dtype;
+
+/* Context and tensors: reference h3_gpu.h:36-96, cuda/h3_gpu_cuda.cu:163-402. */
+h3_gpu *h3_gpu_create(const char *shader_source_path, char *error, size_t error_size);
+void h3_gpu_free(h3_gpu *gpu);
+h3_gpu_tensor *h3_gpu_tensor_new_f32(h3_gpu *gpu, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_new_bf16(h3_gpu *gpu, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_from_f32(h3_gpu *gpu, const float *values, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_from_bf16(h3_gpu *gpu, const uint16_t *values, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_from_u32(h3_gpu *gpu, const uint32_t *values, size_t elements);
+void h3_gpu_tensor_free(h3_gpu_tensor *tensor);
+size_t h3_gpu_tensor_elements(const h3_gpu_tensor *tensor);
+h3_gpu_dtype h3_gpu_tensor_dtype(const h3_gpu_tensor *tensor);
+int h3_gpu_tensor_read_f32(const h3_gpu_tensor *tensor, float *values, size_t elements);
+int h3_gpu_tensor_read_bf16(const h3_gpu_tensor *tensor, uint16_t *values, size_t elements);
+int h3_gpu_tensor_write_f32(h3_gpu_tensor *tensor, const float *values, size_t elements);
+int h3_gpu_tensor_write_bf16(h3_gpu_tensor *tensor, const uint16_t *values, size_t elements);
+int h3_gpu_tensor_write_bf16_range(h3_gpu_tensor *tensor, size_t destination_offset,
+                                   const uint16_t *values, size_t elements);
+int h3_gpu_begin(h3_gpu *gpu);
+int h3_gpu_continue(h3_gpu *gpu);
+int h3_gpu_submit(h3_gpu *gpu);
+const char *h3_gpu_error(const h3_gpu *gpu);
+int h3_gpu_zero(h3_gpu *gpu, h3_gpu_tensor *tensor); /* cuda/parallel.cuh:155-157 */
+int h3_gpu_copy_bf16(h3_gpu *gpu, h3_gpu_tensor *destination, size_t destination_offset,
+                     const h3_gpu_tensor *source, size_t source_offset,
+                     size_t elements); /* h3_gpu.h:132-135 */
+int h3_gpu_download(h3_gpu *gpu, const h3_gpu_tensor *tensor, size_t offset, void *host,
+                    size_t count); /* cuda/h3_cuda.h:55-56; offset and count in bytes */
+
+/* Dense attention: reference h3_gpu.h:494-497 -> cuda/h3_gpu_cuda.cu:1109-1130,1216-1220.
+ * Q, K, V, O are [sequence][heads][128] bf16; head_dim must be 128. */
+int h3_gpu_sdpa_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                     const h3_gpu_tensor *key, const h3_gpu_tensor *value, uint32_t sequence,
+                     uint32_t heads, uint32_t head_dim, float scale);
+/* cuda/h3_cuda.h:78-81 -> cuda/h3_gpu_cuda.cu:1242-1246 (always the h3_flash_bf16 path). */
+int h3_gpu_sdpa_fa2_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                         const h3_gpu_tensor *key, const h3_gpu_tensor *value, uint32_t tokens,
+                         uint32_t heads, uint32_t head_dim, float scale);
+/* h3_gpu.h:534-540: causal grouped-query attention (text encoder). */
+int h3_gpu_gqa_causal_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                           const h3_gpu_tensor *key, const h3_gpu_tensor *value,
+                           uint32_t sequence, uint32_t query_heads, uint32_t kv_heads,
+                           uint32_t head_dim, float scale);
+/* cuda/h3_cuda.h:202-205 -> cuda/vae_fp16.cuh:275-296: fp16, head dim 64. */
+int h3_gpu_sdpa_f16_d64(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                        const h3_gpu_tensor *key, const h3_gpu_tensor *value, uint32_t tokens,
+                        uint32_t heads, uint32_t head_dim, float scale);
+/* cuda/h3_cuda.h:16-19 -> cuda/h3_gpu_cuda.cu:1221-1241: live-mode rectangular attention
+ * over row slices; scale is fixed at 1/sqrt(128). */
+int h3_gpu_cross_attention_bf16(h3_gpu *gpu, h3_gpu_tensor *out, size_t out_row,
+                                const h3_gpu_tensor *q, size_t q_row, const h3_gpu_tensor *k,
+                                const h3_gpu_tensor *v, size_t kv_row, uint32_t query_rows,
+                                uint32_t key_rows, uint32_t heads);
+
+/* Video sparse attention: cuda/h3_cuda.h:70-76 -> cuda/vsa.cuh:192-300. */
+h3_gpu_vsa *h3_gpu_vsa_new(h3_gpu *gpu, uint32_t text_rows, uint32_t audio_rows, uint32_t time,
+                           uint32_t height, uint32_t width, uint32_t heads);
+void h3_gpu_vsa_free(h3_gpu_vsa *vsa);
+int h3_gpu_vsa_bf16(h3_gpu_vsa *vsa, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                    const h3_gpu_tensor *key, const h3_gpu_tensor *value,
+                    const h3_gpu_tensor *gate);
+
+/* Multi-GPU, Ulysses sequence parallelism: cuda/h3_cuda.h:20-39 -> cuda/parallel.cuh:25-153. */
+int h3_gpu_device_count(void);
+int h3_gpu_select_device(int device, char *error, size_t error_size);
+int h3_gpu_comm_init_all(int count, h3_gpu_comm **comms, char *error, size_t error_size);
+void h3_gpu_comm_free(h3_gpu_comm *comm);
+void h3_gpu_comm_abort(h3_gpu_comm *comm);
+int h3_gpu_ulysses_scatter_heads_bf16(h3_gpu *gpu, h3_gpu_comm *comm, h3_gpu_tensor *tensor,
+                                      h3_gpu_tensor *scratch, uint32_t rows, uint32_t heads,
+                                      uint32_t dim);
+int h3_gpu_ulysses_gather_heads_bf16(h3_gpu *gpu, h3_gpu_comm *comm, h3_gpu_tensor *tensor,
+                                     h3_gpu_tensor *scratch, uint32_t rows, uint32_t heads,
+                                     uint32_t dim);
+int h3_gpu_all_gather_bf16(h3_gpu *gpu, h3_gpu_comm *comm, h3_gpu_tensor *output,
+                           const h3_gpu_tensor *input, size_t count);
+
+/* ------------------------------------------------------------------------------------
+ * 3. Additions (no counterpart in the reference).
+ * ------------------------------------------------------------------------------------ */
+
+/* Device status word of the current device: 0 = ok, 1 = a bounded device-side wait gave
+ * up, 2 = a device-side bounds check refused an access. Synchronises the device.
+ * reset != 0 clears the word after reading. */
+cudaError_t h3b_device_status(int *status, int reset);
+
+/* Wrap device memory the caller owns (e.g. a framework tensor) as a non-owning
+ * h3_gpu_tensor; h3_gpu_tensor_free releases only the handle. */
+h3_gpu_tensor *h3b_tensor_wrap(h3_gpu *gpu, void *device_pointer, size_t elements,
+                               h3_gpu_dtype dtype);
+h3_gpu_tensor *h3b_tensor_new_f16(h3_gpu *gpu, size_t elements);
+void *h3b_tensor_data(const h3_gpu_tensor *tensor);
+/* Run the context on a caller-owned stream (NULL restores the context's own stream). */
+int h3b_gpu_set_stream(h3_gpu *gpu, cudaStream_t stream);
+cudaStream_t h3b_gpu_stream(const h3_gpu *gpu);
+
+/* One-process-per-GPU communicator: rank 0 calls h3b_comm_unique_id, ships the 128 bytes
+ * to the other ranks by any means, then every rank calls h3b_comm_init_rank. */
+int h3b_comm_unique_id(void *id128, char *error, size_t error_size);
+int h3b_comm_init_rank(const void *id128, int rank, int count, h3_gpu_comm **comm, char *error,
+                       size_t error_size);
+int h3b_comm_rank(const h3_gpu_comm *comm);
+int h3b_comm_size(const h3_gpu_comm *comm);
+
+/* VSA introspection for tests and tools: geometry, an override for the number of kept
+ * video tiles (the reference fixes ceil(10 %)), and device pointers of the work buffers
+ * of the last h3_gpu_vsa_bf16 call. which: 0 map, 1 sizes, 2-4 tiled q/k/v, 5 sparse out,
+ * 6-8 pooled q/k/v, 9 indices, 10 counts, 11 compression, 12 scores (only when tracing). */
+int h3b_vsa_info(const h3_gpu_vsa *vsa, int *rows, int *tiles, int *prefix, int *keep);
+int h3b_vsa_set_keep(h3_gpu_vsa *vsa, int keep);
+int h3b_vsa_trace_scores(h3_gpu_vsa *vsa, int enable);
+void *h3b_vsa_buffer(const h3_gpu_vsa *vsa, int which);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* H3B200_ATTN_H */

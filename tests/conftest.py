@@ -1,0 +1,61 @@
+"""Shared fixtures. GPU tests are marked `gpu`; everything else runs on CPU."""
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a B200 GPU and the built CUDA library")
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    module = entry.load_oracle()
+    module.build()
+    return module
+
+
+@pytest.fixture(scope="session")
+def package():
+    return entry.load_package()
+
+
+@pytest.fixture(scope="session")
+def gpu(package):
+    """One h3_gpu context for the whole session. The library has no CPU path: if the CUDA
+    library or a B200 is missing this raises and every GPU test errors."""
+    package.build()
+    from h3_omni_b200 import native
+    context = native.Native()
+    yield context
+    context.close()
+
+
+def metrics(got, want):
+    """max-abs, cosine and relative L2 between two float arrays."""
+    got = np.asarray(got, dtype=np.float64).ravel()
+    want = np.asarray(want, dtype=np.float64).ravel()
+    diff = got - want
+    return dict(
+        max_abs=float(np.abs(diff).max()),
+        cosine=float(got @ want / (np.linalg.norm(got) * np.linalg.norm(want) + 1e-300)),
+        rel_l2=float(np.linalg.norm(diff) / (np.linalg.norm(want) + 1e-300)),
+    )
+
+
+# Acceptance: max-abs <= 1e-2 and cosine >= 0.9999 against an fp32 recomputation (the stated
+# target for this path), plus the reference's own bf16 limit rel-L2 < 0.008
+# (reference tests/pytorch/acceptance.json:5-8).
+def assert_attention_close(got_bf16_as_f32, want_f32, max_abs=1e-2, cosine=0.9999, rel_l2=0.008):
+    m = metrics(got_bf16_as_f32, want_f32)
+    assert np.isfinite(got_bf16_as_f32).all(), "non-finite output"
+    assert m["max_abs"] <= max_abs, m
+    assert m["cosine"] >= cosine, m
+    assert m["rel_l2"] <= rel_l2, m
+    return m

@@ -1,0 +1,221 @@
+"""Dense, rectangular, causal/GQA and fp16 attention through the C ABI against the CPU oracle.
+
+Shapes follow the reference's own primitive tests (tests/pytorch/primitives.py:93-136: odd
+lengths 7/128/263, GQA, causal) and its live-mode test (tests/live/attention.py:16-38: the
+two-call text/media pattern with row offsets), plus tile-boundary lengths for the 128-row
+tcgen05 tiles.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from conftest import assert_attention_close
+
+pytestmark = pytest.mark.gpu
+SCALE = float(1.0 / np.sqrt(128.0))
+
+
+def run_sdpa(gpu, oracle, L, H, seed, primitive="sdpa_bf16"):
+    q, k, v = (oracle.normal_bf16((1, L, H, 128), seed + i) for i in range(3))
+    ty = gpu.empty_bf16(q.size)
+    tq, tk, tv = gpu.tensor(q), gpu.tensor(k), gpu.tensor(v)
+    gpu.call(primitive, ty, tq, tk, tv, L, H, 128, SCALE)
+    got = oracle.from_bf16(gpu.read(ty, q.shape))
+    want, _ = oracle.attention(q, k, v, SCALE)
+    for t in (ty, tq, tk, tv):
+        gpu.free(t)
+    return got, want
+
+
+@pytest.mark.parametrize("L", [1, 7, 63, 64, 65, 127, 128, 129, 255, 256, 257, 263, 300, 1000])
+def test_sdpa_bf16_lengths(gpu, oracle, L):
+    got, want = run_sdpa(gpu, oracle, L, 3, 100 + L)
+    assert_attention_close(got, want)
+    assert gpu.device_status() == 0
+
+
+@pytest.mark.parametrize("L,H", [(2048, 8), (1536, 56), (4096, 2)])
+def test_sdpa_bf16_larger(gpu, oracle, L, H):
+    got, want = run_sdpa(gpu, oracle, L, H, 7 * L + H)
+    assert_attention_close(got, want)
+    assert gpu.device_status() == 0
+
+
+def test_sdpa_fa2_entry_matches_flash3_entry(gpu, oracle):
+    """h3_gpu_sdpa_fa2_bf16 (FlashAttention-2 adapter path) and h3_gpu_sdpa_bf16 agree."""
+    a, want = run_sdpa(gpu, oracle, 263, 4, 5, "sdpa_bf16")
+    b, _ = run_sdpa(gpu, oracle, 263, 4, 5, "sdpa_fa2_bf16")
+    assert_attention_close(b, want)
+    assert np.array_equal(a, b)
+
+
+def test_sdpa_uniform_distribution(gpu, oracle):
+    """Second input distribution of the reference's attention microbenchmark
+    (tests/serving/profile/attn_bench.cu:95-98): Q, K ~ U(-2, 2), V ~ U(-1, 1)."""
+    rng = np.random.default_rng(99)
+    L, H = 700, 4
+    q = oracle.to_bf16(rng.uniform(-2, 2, (1, L, H, 128)))
+    k = oracle.to_bf16(rng.uniform(-2, 2, (1, L, H, 128)))
+    v = oracle.to_bf16(rng.uniform(-1, 1, (1, L, H, 128)))
+    ty = gpu.empty_bf16(q.size)
+    gpu.call("sdpa_bf16", ty, gpu.tensor(q), gpu.tensor(k), gpu.tensor(v), L, H, 128, SCALE)
+    got = oracle.from_bf16(gpu.read(ty, q.shape))
+    want, _ = oracle.attention(q, k, v, SCALE)
+    assert_attention_close(got, want)
+
+
+def test_sdpa_large_logits_rescale(gpu, oracle):
+    """Rows whose maximum keeps growing exercise the lazy accumulator rescale."""
+    L, H = 640, 2
+    q = oracle.normal_bf16((1, L, H, 128), 41, 3.0)
+    k = oracle.from_bf16(oracle.normal_bf16((1, L, H, 128), 42, 1.0))
+    k *= np.linspace(0.2, 4.0, L, dtype=np.float32)[None, :, None, None]  # later keys larger
+    k = oracle.to_bf16(k)
+    v = oracle.normal_bf16((1, L, H, 128), 43)
+    ty = gpu.empty_bf16(q.size)
+    gpu.call("sdpa_bf16", ty, gpu.tensor(q), gpu.tensor(k), gpu.tensor(v), L, H, 128, SCALE)
+    got = oracle.from_bf16(gpu.read(ty, q.shape))
+    want, _ = oracle.attention(q, k, v, SCALE)
+    assert_attention_close(got, want, max_abs=2e-2)
+
+
+@pytest.mark.parametrize("L,H,KH", [(7, 8, 2), (128, 8, 2), (263, 8, 4), (263, 6, 1)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_flash_bf16_gqa_causal(gpu, oracle, L, H, KH, causal):
+    """h3_flash_bf16 directly: causal and grouped-query, batch 2, with logsumexp."""
+    B = 2
+    q = oracle.normal_bf16((B, L, H, 128), 1000 + L)
+    k = oracle.normal_bf16((B, L, KH, 128), 2000 + L)
+    v = oracle.normal_bf16((B, L, KH, 128), 3000 + L)
+    ty = gpu.empty_bf16(q.size)
+    tq, tk, tv = gpu.tensor(q), gpu.tensor(k), gpu.tensor(v)
+    tl = gpu.tensor(np.zeros((B, H, L), dtype=np.float32))
+    data = gpu.lib.h3b_tensor_data
+    gpu.raw("h3_flash_bf16", data(ty), data(tq), data(tk), data(tv), data(tl), B, L, H, KH, SCALE,
+            causal, gpu.lib.h3b_gpu_stream(gpu.gpu))
+    got = oracle.from_bf16(gpu.read(ty, q.shape))
+    lse = gpu.read(tl, (B, H, L), np.float32)
+    want, _, want_lse = oracle.attention(q, k, v, SCALE, causal=causal, want_lse=True)
+    assert_attention_close(got, want)
+    assert np.abs(lse - want_lse).max() < 2e-3
+    assert gpu.device_status() == 0
+
+
+def test_gqa_causal_primitive(gpu, oracle):
+    """h3_gpu_gqa_causal_bf16 (reference h3_gpu.h:534-540), the text-encoder call."""
+    L, H, KH = 150, 16, 2
+    q = oracle.normal_bf16((1, L, H, 128), 1)
+    k = oracle.normal_bf16((1, L, KH, 128), 2)
+    v = oracle.normal_bf16((1, L, KH, 128), 3)
+    ty = gpu.empty_bf16(q.size)
+    gpu.call("gqa_causal_bf16", ty, gpu.tensor(q), gpu.tensor(k), gpu.tensor(v), L, H, KH, 128, SCALE)
+    got = oracle.from_bf16(gpu.read(ty, q.shape))
+    want, _ = oracle.attention(q, k, v, SCALE, causal=True)
+    assert_attention_close(got, want)
+
+
+@pytest.mark.parametrize("L,H", [(7, 2), (64, 3), (263, 4), (1030, 2)])
+def test_sdpa_f16_d64(gpu, oracle, L, H):
+    """h3_gpu_sdpa_f16_d64: fp16, head dim 64 (video VAE call, reference cuda/vae_fp16.cuh:275-296)."""
+    from h3_omni_b200 import native
+    rng = np.random.default_rng(L)
+    q, k, v = (oracle.to_f16(rng.standard_normal((1, L, H, 64))) for _ in range(3))
+    ty = gpu.empty_f16(q.size)
+    gpu.call("sdpa_f16_d64", ty, gpu.tensor(q, native.F16), gpu.tensor(k, native.F16),
+             gpu.tensor(v, native.F16), L, H, 64, 0.125)
+    got = oracle.from_f16(gpu.read(ty, q.shape))
+    want, _ = oracle.attention(q, k, v, 0.125, elem="f16")
+    assert_attention_close(got, want, max_abs=5e-3, rel_l2=0.004)
+
+
+def test_sdpa_rejects_bad_arguments(gpu, oracle):
+    """Error behaviour of the primitive layer: 0 + message, no launch."""
+    q = gpu.tensor(oracle.normal_bf16((4, 2, 128), 1))
+    f = gpu.tensor(np.zeros(4 * 2 * 128, dtype=np.float32))
+    y = gpu.empty_bf16(4 * 2 * 128)
+    with pytest.raises(RuntimeError, match="need 2048 elements"):
+        gpu.call("sdpa_bf16", y, q, q, q, 8, 2, 128, SCALE)
+    with pytest.raises(RuntimeError, match="expected BF16"):
+        gpu.call("sdpa_bf16", y, f, q, q, 4, 2, 128, SCALE)
+    with pytest.raises(RuntimeError, match="head dimension 128"):
+        gpu.call("sdpa_bf16", y, q, q, q, 4, 4, 64, SCALE)
+    assert gpu.lib.h3_flash3_bf16(None, None, None, None, None, 1, 4, 2, 2, SCALE, None) != 0
+    assert gpu.lib.h3_flash3_bf16(gpu.lib.h3b_tensor_data(y), gpu.lib.h3b_tensor_data(q),
+                                  gpu.lib.h3b_tensor_data(q), gpu.lib.h3b_tensor_data(q), None, 1,
+                                  4, 3, 2, SCALE, None) != 0  # 3 heads do not group over 2
+
+
+def live_case(gpu, oracle, text, media, history, H, seed):
+    """Two-call live pattern (reference h3_dit_live.inc:88-99, tests/live/attention.py:16-38):
+    K/V rows are [text | history | current media]; text queries attend text only, media
+    queries attend everything."""
+    total_q = text + media
+    total_k = text + history + media
+    q = oracle.normal_bf16((total_q, H, 128), seed)
+    k = oracle.normal_bf16((total_k, H, 128), seed + 1)
+    v = oracle.normal_bf16((total_k, H, 128), seed + 2)
+    tq, tk, tv = gpu.tensor(q), gpu.tensor(k), gpu.tensor(v)
+    ty = gpu.tensor(np.zeros(q.shape, dtype=np.uint16))
+    gpu.call("cross_attention_bf16", ty, 0, tq, 0, tk, tv, 0, text, text, H)
+    gpu.call("cross_attention_bf16", ty, text, tq, text, tk, tv, 0, media, total_k, H)
+    got = oracle.from_bf16(gpu.read(ty, q.shape))
+    want_text, _ = oracle.attention(q[None, :text], k[None, :text], v[None, :text], SCALE)
+    want_media, _ = oracle.attention(q[None, text:], k[None], v[None], SCALE)
+    want = np.concatenate([want_text[0], want_media[0]])
+    return got, want
+
+
+@pytest.mark.parametrize("text,media,history,H", [(17, 100, 0, 4), (77, 300, 500, 4),
+                                                   (128, 405, 1215, 7), (5, 64, 3000, 2)])
+def test_live_cross_attention(gpu, oracle, text, media, history, H):
+    got, want = live_case(gpu, oracle, text, media, history, H, text + media)
+    m = assert_attention_close(got, want)
+    assert m["rel_l2"] < 0.004  # the reference's own limit, tests/live/attention.py:38
+    assert gpu.device_status() == 0
+
+
+def test_cross_attention_row_offsets_leave_other_rows(gpu, oracle):
+    """Output rows outside [out_row, out_row + query_rows) are not touched."""
+    H = 2
+    q = oracle.normal_bf16((300, H, 128), 5)
+    k = oracle.normal_bf16((400, H, 128), 6)
+    v = oracle.normal_bf16((400, H, 128), 7)
+    sentinel = np.full((300, H, 128), 0x7fc0, dtype=np.uint16)
+    ty = gpu.tensor(sentinel)
+    gpu.call("cross_attention_bf16", ty, 50, gpu.tensor(q), 20, gpu.tensor(k), gpu.tensor(v), 100,
+             130, 250, H)
+    out = gpu.read(ty, q.shape)
+    assert np.array_equal(out[:50], sentinel[:50]) and np.array_equal(out[180:], sentinel[180:])
+    want, _ = oracle.attention(q[None, 20:150], k[None, 100:350], v[None, 100:350], SCALE)
+    assert_attention_close(oracle.from_bf16(out[50:180]), want[0])
+
+
+def test_head_split_is_bit_exact(gpu, oracle):
+    """Attention over all heads equals the concatenation of per-half calls bit for bit
+    (reference tests/live/sharding.py:38-46): no cross-head arithmetic anywhere."""
+    L, H = 333, 8
+    q, k, v = (oracle.normal_bf16((L, H, 128), 70 + i) for i in range(3))
+    ty = gpu.empty_bf16(q.size)
+    gpu.call("sdpa_bf16", ty, gpu.tensor(q), gpu.tensor(k), gpu.tensor(v), L, H, 128, SCALE)
+    full = gpu.read(ty, q.shape)
+    halves = []
+    for lo in (0, H // 2):
+        sl = slice(lo, lo + H // 2)
+        th = gpu.empty_bf16(L * (H // 2) * 128)
+        gpu.call("sdpa_bf16", th, gpu.tensor(q[:, sl]), gpu.tensor(k[:, sl]), gpu.tensor(v[:, sl]),
+                 L, H // 2, 128, SCALE)
+        halves.append(gpu.read(th, (L, H // 2, 128)))
+    assert np.array_equal(full, np.concatenate(halves, axis=1))
+
+
+def test_run_twice_is_deterministic(gpu, oracle):
+    L, H = 517, 3
+    q, k, v = (oracle.normal_bf16((L, H, 128), 80 + i) for i in range(3))
+    tq, tk, tv = gpu.tensor(q), gpu.tensor(k), gpu.tensor(v)
+    outs = []
+    for _ in range(2):
+        ty = gpu.empty_bf16(q.size)
+        gpu.call("sdpa_bf16", ty, tq, tk, tv, L, H, 128, SCALE)
+        outs.append(gpu.read(ty, q.shape))
+    assert np.array_equal(outs[0], outs[1])
