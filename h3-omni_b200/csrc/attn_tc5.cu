@@ -155,19 +155,19 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     };
     Walk walk{-1, 0u};
     auto next_tile = [&](int j, int &kt, int &flags) {
-        if (!SPARSE) {
+        if constexpr (!SPARSE) {
             kt = j;
             flags = 3;
-            return;
+        } else {
+            while (walk.cur == 0u) {
+                walk.word++;
+                walk.cur = bits_a[walk.word] | bits_b[walk.word];
+            }
+            const int b = __ffs(walk.cur) - 1;
+            walk.cur &= walk.cur - 1;
+            kt = walk.word * 32 + b;
+            flags = ((bits_a[walk.word] >> b) & 1u) | (((bits_b[walk.word] >> b) & 1u) << 1);
         }
-        while (walk.cur == 0u) {
-            walk.word++;
-            walk.cur = bits_a[walk.word] | bits_b[walk.word];
-        }
-        const int b = __ffs(walk.cur) - 1;
-        walk.cur &= walk.cur - 1;
-        kt = walk.word * 32 + b;
-        flags = ((bits_a[walk.word] >> b) & 1u) | (((bits_b[walk.word] >> b) & 1u) << 1);
     };
 
     if (warp == 4) {
@@ -293,6 +293,10 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             }
             const float m_new = fmaxf(m_ref, mx);
             const bool grow = (m_new - m_ref) * p.scale_log2 > RESCALE_LOG2;
+            // Every thread observes every phase of pv_done exactly once and in order (phase
+            // j-1 during iteration j), so a parity wait can never alias a phase two behind:
+            // PV(j) cannot complete before this thread has delivered P(j).
+            bool saw_prev_pv = (j == 0);
             if (__any_sync(0xffffffffu, grow)) {
                 const float alpha = grow ? fast_exp2((m_ref - m_new) * p.scale_log2) : 1.0f;
                 if (grow) m_ref = m_new;
@@ -301,6 +305,7 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                     alive = __all_sync(0xffffffffu,
                                        mbar_wait(bar_pv_done, (j - 1) & 1, &abort_word));
                     if (!alive) break;
+                    saw_prev_pv = true;
                     tc5_fence_after();
 #pragma unroll
                     for (int c = 0; c < HD / 32; c++) {
@@ -333,6 +338,10 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                     packed[i / 2] = pack_bf16(p0, p1);
                 }
                 tmem_st16(s_addr + c * 16, packed);
+            }
+            if (!saw_prev_pv) {
+                alive = __all_sync(0xffffffffu, mbar_wait(bar_pv_done, (j - 1) & 1, &abort_word));
+                if (!alive) break;
             }
             tmem_wait_st();
             tc5_fence_before();
