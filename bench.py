@@ -1,0 +1,419 @@
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A step is one joint video+audio dense self-attention forward over the 5 s, 864x480 block shape
+(52,352 tokens, 24 heads, head dim 128, bf16) - at N GPUs the same sequence is row-sharded and
+every step also runs the Ulysses head-scatter of Q, K, V and the sequence-gather of O, so the
+numbers at N = 1, 2, 4, 8 are one strong-scaling series. Inputs are seeded synthetic N(0,1)
+tensors. One JSON line is printed by rank 0.
+
+Other workloads (--workload vsa | live) time the sparse and the KV-history paths on the same
+contract; they are reported under "also" in the default run.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+SEQ_VIDEO, SEQ_AUDIO, HEADS, DIM = 51840, 512, 24, 128
+SEQ = SEQ_VIDEO + SEQ_AUDIO
+SCALE = float(1.0 / np.sqrt(128.0))
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dense kernel at the full
+# workload, scaled from the ncu capture summarised in profiles/ (None until captured).
+DENSE_TRAFFIC_BYTES = None
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return dict(tflops=d["bf16_tflops"], tflops_sustained=d["bf16_tflops_sustained"],
+                    hbm_gbs=d["hbm_gbs"], source="measured")
+    return dict(tflops=1590.0, tflops_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms during the timed region."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(device_index), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "200"], stdout=self.file,
+                stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        rows = [line.split(",") for line in Path(self.file.name).read_text().splitlines() if line.count(",") >= 8]
+        os.unlink(self.file.name)
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(float(r[1]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any("Active" == r[5 + i].strip() for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][2]), "reasons": reasons,
+                "samples": len(rows), "power_w_max": max(float(r[3]) for r in rows)}
+
+
+def cpu_sample(oracle, seed_base=1002, rows=256):
+    """CPU baseline on a bounded sample: the first `rows` query rows of the dense workload
+    against all keys, all heads, on every host core. Returns (TFLOP/s, description, cores)."""
+    q = oracle.normal_bf16((rows, HEADS, DIM), seed_base)
+    k = oracle.normal_bf16((SEQ, HEADS, DIM), seed_base + 1)
+    v = oracle.normal_bf16((SEQ, HEADS, DIM), seed_base + 2)
+    seconds = oracle.time_attention(q, k, v, SCALE)
+    flops = 4.0 * rows * SEQ * HEADS * DIM
+    sample = "first %d of %d query rows x %d keys x %d heads (%.1f GFLOP), CPU oracle, OpenMP" % (
+        rows, SEQ, SEQ, HEADS, flops / 1e9)
+    return flops / seconds / 1e12, seconds, sample, os.cpu_count()
+
+
+def run_reference(args):
+    """The reference has no CPU attention path; its arm is the CPU oracle (a port of the
+    reference's FP32 attention arithmetic) on all host threads, on a bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    oracle = entry.load_oracle()
+    oracle.build()
+    values = []
+    for i in range(args.warmup + args.steps):
+        tflops, seconds, sample, cores = cpu_sample(oracle, rows=64)
+        if i >= args.warmup:
+            values.append((tflops, seconds))
+    value = float(np.mean([v[0] for v in values]))
+    ms = float(np.mean([v[1] for v in values])) * 1e3
+    line = {
+        "impl": "reference", "metric": "attn_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n):
+    return {"workload": "dense joint video+audio attention, one 5 s 864x480 DiT block: "
+                        "L=52352 (512 audio + 51840 video), H=24, D=128, bf16, scale 1/sqrt(128), no mask",
+            "sequence": SEQ, "heads": HEADS, "head_dim": DIM,
+            "parallelism": "single GPU" if n == 1 else "ulysses sp%d (head-scatter/sequence-gather all-to-all)" % n,
+            "l2": "inputs (965 MB) larger than L2 (126 MB); no flush between steps"}
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--workload", default="dense", choices=["dense", "vsa", "live"])
+    parser.add_argument("--no-also", action="store_true", help="skip the secondary measurements")
+    parser.add_argument("--sequence", type=int, default=0, help="override L (profiling on small cases)")
+    parser.add_argument("--heads", type=int, default=0, help="override H (profiling on small cases)")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+
+    entry.load_package()
+    from h3_omni_b200 import native, ulysses
+
+    global SEQ, HEADS
+    if args.sequence:
+        SEQ = args.sequence
+    if args.heads:
+        HEADS = args.heads
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d: launch with torch.distributed.run" % (args.gpus, world))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    gpu = native.Native()
+    lib = gpu.lib
+    # One explicit stream for copies, kernels, exchanges and the timing events.
+    stream = torch.cuda.Stream(device)
+    torch.cuda.set_stream(stream)
+    lib.h3b_gpu_set_stream(gpu.gpu, C.c_void_p(stream.cuda_stream))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    comm = None
+    if world > 1:
+        ident = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = (C.c_ubyte * 128)()
+            err = C.create_string_buffer(256)
+            if not lib.h3b_comm_unique_id(buf, err, 256):
+                raise RuntimeError(err.value.decode())
+            ident = torch.tensor(list(buf), dtype=torch.uint8)
+        ident = ident.to(device)
+        dist.broadcast(ident, 0)
+        raw = bytes(ident.cpu().tolist())
+        handle = C.c_void_p()
+        err = C.create_string_buffer(256)
+        if not lib.h3b_comm_init_rank(raw, rank, world, C.byref(handle), err, 256):
+            raise RuntimeError(err.value.decode())
+        comm = handle
+
+    plan = ulysses.plan(SEQ, HEADS, world)
+    rows, local_heads = plan.shard_rows, plan.local_heads
+    shard_elems = rows * HEADS * DIM
+
+    # Seeded synthetic inputs: the full tensors are defined by (seed, element index); each rank
+    # generates its own row shard. Host copies live in pinned memory for the end-to-end leg.
+    def make_shard(seed):
+        g = torch.Generator(device="cpu")
+        g.manual_seed(seed * 1000 + rank)
+        x = torch.randn(rows, HEADS, DIM, generator=g, dtype=torch.float32).to(torch.bfloat16)
+        if plan.valid_rows(rank) < rows:
+            x[plan.valid_rows(rank):] = 0
+        return x.pin_memory()
+
+    host_q, host_k, host_v = make_shard(1002), make_shard(1003), make_shard(1004)
+    host_o = torch.empty(rows, HEADS, DIM, dtype=torch.bfloat16).pin_memory()
+    dq, dk, dv = (x.to(device, non_blocking=True) for x in (host_q, host_k, host_v))
+    do = torch.empty_like(dq)
+    scratch = torch.empty_like(dq) if world > 1 else None
+    work = [torch.empty_like(dq) for _ in range(3)] if world > 1 else None
+    torch.cuda.synchronize()
+
+    wrap = lambda t: gpu.wrap(t.data_ptr(), t.numel())
+    tq, tk, tv, to = wrap(dq), wrap(dk), wrap(dv), wrap(do)
+    if world > 1:
+        tscr = wrap(scratch)
+        tw = [wrap(w) for w in work]
+
+    launches = [0]
+
+    def attention_step():
+        """The hot path with inputs resident in HBM."""
+        if world == 1:
+            gpu.call("sdpa_bf16", to, tq, tk, tv, SEQ, HEADS, DIM, SCALE)
+            launches[0] += 1
+            return
+        # the exchange is in place, so each step scatters a fresh copy of the row shards
+        for w, src in zip(work, (dq, dk, dv)):
+            w.copy_(src, non_blocking=True)
+        for t in tw:
+            gpu.call("ulysses_scatter_heads_bf16", comm, t, tscr, rows, HEADS, DIM)
+        gpu.call("sdpa_bf16", to, tw[0], tw[1], tw[2], SEQ, local_heads, DIM, SCALE)
+        gpu.call("ulysses_gather_heads_bf16", comm, to, tscr, rows, HEADS, DIM)
+        launches[0] += 5
+
+    def e2e_step():
+        """The same step through the public API with host buffers."""
+        dq.copy_(host_q, non_blocking=True)
+        dk.copy_(host_k, non_blocking=True)
+        dv.copy_(host_v, non_blocking=True)
+        attention_step()
+        host_o.copy_(do, non_blocking=True)
+        stream.synchronize()
+
+    flops = 4.0 * SEQ * SEQ * HEADS * DIM
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(steps):
+            fn()
+        stop.record(stream)
+        barrier()
+        return max_over_ranks(start.elapsed_time(stop) / steps)
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches[0] = 0
+    ms = timed(attention_step, args.steps, args.warmup)
+    counted = launches[0] * args.steps // (args.steps + args.warmup)
+    clocks = sampler.stop() if sampler else None
+
+    # kernel-only duration of the dense kernel (the dominant kernel), events on its own stream
+    def kernel_only():
+        if world == 1:
+            return ms
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record(stream)
+        for _ in range(args.steps):
+            gpu.call("sdpa_bf16", to, tw[0], tw[1], tw[2], SEQ, local_heads, DIM, SCALE)
+        stop.record(stream)
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / args.steps
+
+    kernel_ms = kernel_only()
+    e2e_ms = timed(e2e_step, max(2, args.steps // 2), 1)
+    status = gpu.device_status()
+    if status:
+        raise SystemExit("device status %d after the timed region" % status)
+
+    pk = peaks()
+    kernel_flops = flops / world
+    achieved = kernel_flops / (kernel_ms * 1e-3) / 1e12
+    line = {
+        "metric": "attn_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(world),
+        "roofline": {"bound": "tensor", "kernel": "attn_tc5_kernel<128,false>", "achieved": achieved,
+                     "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
+                     "peak_source": pk["source"] + " burst", "frac_of_sustained": achieved / pk["tflops_sustained"],
+                     "frac_of_nominal_2250": achieved / 2250.0, "kernel_ms": kernel_ms,
+                     "flops_per_launch": kernel_flops, "traffic": DENSE_TRAFFIC_BYTES},
+        "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": 3 * shard_elems * 2, "d2h_bytes_per_step": shard_elems * 2},
+        "gpu_launches": counted,
+        "clocks": clocks,
+    }
+
+    if rank == 0 and world == 1:
+        oracle = entry.load_oracle()
+        oracle.build()
+        tflops, seconds, sample, cores = cpu_sample(oracle)
+        line["cpu_baseline"] = {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                "sample": sample, "seconds": seconds}
+        if not args.no_also and not args.sequence:
+            line["also"] = secondary(gpu, torch, device, stream, pk)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if comm is not None:
+        lib.h3_gpu_comm_free(comm)
+    gpu.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def secondary(gpu, torch, device, stream, pk):
+    """VSA (coarse + fine + merge) and live KV-history attention on the benchmark shapes."""
+    out = {}
+    lib = gpu.lib
+
+    def events(fn, steps=5, warmup=2):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(steps):
+            fn()
+        b.record(stream)
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    # --- VSA: text 64 + audio 512 prefix, video 32x30x54 -> 896 cubes, keep 12.5 % ---
+    text, audio, grid = 64, 512, (32, 30, 54)
+    vsa = gpu.call("vsa_new", text, audio, *grid, HEADS)
+    info = [C.c_int() for _ in range(4)]
+    lib.h3b_vsa_info(vsa, *[C.byref(x) for x in info])
+    rows, tiles, prefix, _ = (x.value for x in info)
+    keep = (tiles - prefix) // 8
+    lib.h3b_vsa_set_keep(vsa, keep)
+    g = torch.Generator(device=device)
+    g.manual_seed(1003)
+    q, k, v = (torch.randn(rows, HEADS, DIM, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+               for _ in range(3))
+    gate = (0.3 * torch.randn(rows, HEADS, DIM, generator=g, device=device)).to(torch.bfloat16)
+    o = torch.empty_like(q)
+    wrap = lambda t: gpu.wrap(t.data_ptr(), t.numel())
+    tq, tk, tv, tg, to = wrap(q), wrap(k), wrap(v), wrap(gate), wrap(o)
+
+    def vsa_step():
+        if not lib.h3_gpu_vsa_bf16(vsa, to, tq, tk, tv, tg):
+            raise RuntimeError(gpu.error())
+
+    total_ms = events(vsa_step)
+    d = lib.h3b_vsa_buffer
+    st = lib.h3b_gpu_stream(gpu.gpu)
+
+    def fine_only():
+        gpu.raw("h3_vsa_hopper", d(vsa, 5), d(vsa, 2), d(vsa, 3), d(vsa, 4), None, d(vsa, 9),
+                d(vsa, 10), d(vsa, 1), tiles, HEADS, st)
+
+    fine_ms = events(fine_only)
+    pairs = (tiles - prefix) * (prefix + keep) + prefix * tiles
+    fine_flops = pairs * 4.0 * 64 * 64 * 128 * HEADS
+    dense_equiv = 4.0 * (tiles * 64) ** 2 * HEADS * DIM
+    coarse_bytes = 5.0 * rows * HEADS * DIM * 2
+    out["vsa"] = {
+        "workload": "text 64 + audio 512 + video 32x30x54, %d tiles (%d prefix), keep %d of %d video tiles, H=%d"
+                    % (tiles, prefix, keep, tiles - prefix, HEADS),
+        "total_ms": total_ms, "fine_ms": fine_ms, "coarse_and_merge_ms": total_ms - fine_ms,
+        "fine_tflops_selected": fine_flops / fine_ms / 1e9, "fine_frac_of_peak": fine_flops / fine_ms / 1e9 / pk["tflops"],
+        "dense_equivalent_tflops": dense_equiv / total_ms / 1e9,
+        "coarse_and_merge_gbs": coarse_bytes / (total_ms - fine_ms) / 1e6,
+        "coarse_frac_of_hbm": coarse_bytes / (total_ms - fine_ms) / 1e6 / pk["hbm_gbs"],
+    }
+    lib.h3_gpu_vsa_free(vsa)
+    del q, k, v, gate, o
+
+    # --- live: 12,960-row query chunk against 12,960 + history keys, history up to 51,840 ---
+    nq = 12960
+    g.manual_seed(1005)
+    kv_rows = nq * 5
+    q = torch.randn(nq, HEADS, DIM, generator=g, device=device).to(torch.bfloat16)
+    k = torch.randn(kv_rows, HEADS, DIM, generator=g, device=device).to(torch.bfloat16)
+    v = torch.randn(kv_rows, HEADS, DIM, generator=g, device=device).to(torch.bfloat16)
+    o = torch.empty_like(q)
+    tq, tk, tv, to = wrap(q), wrap(k), wrap(v), wrap(o)
+    steps = []
+    for s in range(12):
+        nk = nq + min(s, 4) * nq
+        ms = events(lambda: gpu.call("cross_attention_bf16", to, 0, tq, 0, tk, tv, 0, nq, nk, HEADS), 3, 1)
+        steps.append({"step": s, "key_rows": nk, "ms": ms, "tflops": 4.0 * nq * nk * HEADS * DIM / ms / 1e9})
+    out["live"] = {"workload": "query chunk 12960 rows, keys 12960 + min(step,4)*12960 history rows, H=%d" % HEADS,
+                   "steps": steps, "total_ms": sum(x["ms"] for x in steps)}
+    return out
+
+
+if __name__ == "__main__":
+    main()

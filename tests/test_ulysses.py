@@ -1,0 +1,118 @@
+"""Ulysses sequence parallelism: host plan and exchange algebra on CPU (gloo, world size 2),
+the in-place scatter/gather primitives on one GPU, and the full multi-rank path on real GPUs
+when the box has more than one."""
+import ctypes as C
+import os
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_plan_matches_reference_sharding(package):
+    from h3_omni_b200 import ulysses
+    p = ulysses.plan(101464, 24, 8)          # 10 s clip: no padding at 2, 4, 8 ranks
+    assert (p.shard_rows, p.local_heads, p.padded_rows) == (12683, 3, 101464)
+    p = ulysses.plan(15400, 56, 7)           # reference-true heads split over 7 ranks
+    assert (p.shard_rows, p.local_heads) == (2200, 8)
+    p = ulysses.plan(1001, 8, 4)             # padded tail lives on the last rank
+    assert p.shard_rows == 251 and [p.valid_rows(r) for r in range(4)] == [251, 251, 251, 248]
+    assert p.exchange_bytes() == 251 * 8 * 128 * 2 * 3 // 4
+    with pytest.raises(ValueError):
+        ulysses.plan(100, 24, 5)
+
+
+def _gloo_rank(rank, world, port, rows, heads, dim, result):
+    """swap_leading + all_to_all exactly as the library orders them, on gloo."""
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    full = torch.arange(world * rows * heads * dim, dtype=torch.int32).reshape(world, rows, heads, dim)
+    mine = full[rank].clone()
+    group = heads // world
+    # scatter: [rows][ranks][group*dim] -> [ranks][rows][group*dim]; block j to rank j
+    send = mine.reshape(rows, world, group * dim).transpose(0, 1).contiguous()
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send)
+    scattered = recv.reshape(world * rows, group, dim)
+    # gather: blocks back, then [ranks][rows][group*dim] -> [rows][ranks][group*dim]
+    back = torch.empty_like(recv)
+    dist.all_to_all_single(back, recv)
+    restored = back.transpose(0, 1).contiguous().reshape(rows, heads, dim)
+    result.put((rank, scattered.numpy().copy(), restored.numpy().copy()))
+    dist.destroy_process_group()
+
+
+def test_exchange_algebra_gloo_world2(oracle):
+    import torch.multiprocessing as mp
+    world, rows, heads, dim = 2, 5, 4, 8
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = 29500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_gloo_rank, args=(r, world, port, rows, heads, dim, result)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted(result.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    full = np.arange(world * rows * heads * dim, dtype=np.int32).reshape(world, rows, heads, dim)
+    want = oracle.ulysses(full.astype(np.uint16))
+    for rank, scattered, restored in got:
+        assert np.array_equal(scattered.astype(np.uint16), want[rank])
+        assert np.array_equal(restored, full[rank])
+
+
+@pytest.mark.gpu
+def test_single_rank_exchange_is_identity(gpu, oracle):
+    comms = (C.c_void_p * 1)()
+    err = C.create_string_buffer(256)
+    assert gpu.lib.h3_gpu_comm_init_all(1, comms, err, 256), err.value
+    comm = C.c_void_p(comms[0])
+    try:
+        rows, heads = 300, 6
+        x = oracle.normal_bf16((rows, heads, 128), 3)
+        t, scratch = gpu.tensor(x), gpu.empty_bf16(x.size)
+        gpu.call("ulysses_scatter_heads_bf16", comm, t, scratch, rows, heads, 128)
+        assert np.array_equal(gpu.read(t, x.shape), x)
+        gpu.call("ulysses_gather_heads_bf16", comm, t, scratch, rows, heads, 128)
+        assert np.array_equal(gpu.read(t, x.shape), x)
+        small = gpu.empty_bf16(16)
+        with pytest.raises(RuntimeError, match="Ulysses scratch"):
+            gpu.call("ulysses_scatter_heads_bf16", comm, t, small, rows, heads, 128)
+    finally:
+        gpu.lib.h3_gpu_comm_free(comm)
+    bad = C.c_void_p()
+    assert not gpu.lib.h3_gpu_comm_init_all(0, None, err, 256)
+    with pytest.raises(RuntimeError, match="do not split"):
+        gpu.call("ulysses_scatter_heads_bf16", None, t, scratch, rows, heads, 128)
+
+
+@pytest.mark.gpu
+def test_multi_rank_scatter_attention_gather(gpu):
+    """One child process per GPU; skipped on a single-GPU box."""
+    count = gpu.lib.h3_gpu_device_count()
+    if count < 2:
+        pytest.skip("needs 2 or more GPUs")
+    world = 4 if count >= 4 else 2
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    with tempfile.TemporaryDirectory() as rdv:
+        procs = [subprocess.Popen([sys.executable, str(ROOT / "tests" / "ulysses_worker.py"), str(r),
+                                   str(world), rdv], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                                  text=True, env=env) for r in range(world)]
+        outputs = []
+        for p in procs:
+            try:
+                out, _ = p.communicate(timeout=300)
+            except subprocess.TimeoutExpired:
+                p.kill()
+                out, _ = p.communicate()
+            outputs.append(out)
+        for r, (p, out) in enumerate(zip(procs, outputs)):
+            assert p.returncode == 0 and "OK rank %d" % r in out, out[-2000:]

@@ -1,0 +1,88 @@
+"""One rank of the multi-GPU Ulysses test (run as a child process per GPU).
+
+usage: ulysses_worker.py RANK WORLD RENDEZVOUS_DIR
+Scatters row shards of Q, K, V, runs attention on this rank's heads over the whole sequence,
+gathers the output, and checks every step against the CPU oracle. Prints "OK" on success.
+"""
+import ctypes as C
+import os
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+
+def main():
+    rank, world, rdv = int(sys.argv[1]), int(sys.argv[2]), Path(sys.argv[3])
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    entry.load_package()
+    from h3_omni_b200 import native, ulysses
+    oracle = entry.load_oracle()
+    lib = native.load_library()
+    err = C.create_string_buffer(256)
+    assert lib.h3_gpu_select_device(rank, err, 256), err.value
+    gpu = native.Native()
+    ident = rdv / "nccl_id"
+    if rank == 0:
+        buf = (C.c_ubyte * 128)()
+        assert lib.h3b_comm_unique_id(buf, err, 256), err.value
+        tmp = rdv / "nccl_id.tmp"
+        tmp.write_bytes(bytes(buf))
+        tmp.rename(ident)
+    deadline = time.time() + 120
+    while not ident.exists():
+        if time.time() > deadline:
+            raise SystemExit("rendezvous timed out")
+        time.sleep(0.05)
+    comm = C.c_void_p()
+    assert lib.h3b_comm_init_rank(ident.read_bytes(), rank, world, C.byref(comm), err, 256), err.value
+    assert lib.h3b_comm_rank(comm) == rank and lib.h3b_comm_size(comm) == world
+
+    L, H, D = 8 * world * 37 + 5, 8, 128   # not a multiple of the rank count: padded tail
+    scale = float(1 / np.sqrt(128.0))
+    plan = ulysses.plan(L, H, world)
+    rows = plan.shard_rows
+    full = [oracle.normal_bf16((plan.padded_rows, H, D), 300 + i) for i in range(3)]
+    for x in full:
+        x[L:] = 0
+    shards = [x.reshape(world, rows, H, D) for x in full]
+    scratch = gpu.empty_bf16(rows * H * D)
+    tensors = [gpu.tensor(s[rank]) for s in shards]
+    for t, s in zip(tensors, shards):
+        gpu.call("ulysses_scatter_heads_bf16", comm, t, scratch, rows, H, D)
+        got = gpu.read(t, (world * rows, H // world, D))
+        assert np.array_equal(got, oracle.ulysses(s)[rank]), "scatter mismatch"
+    out = gpu.empty_bf16(rows * H * D)
+    gpu.call("zero", out)
+    gpu.call("sdpa_bf16", out, *tensors, L, plan.local_heads, D, scale)
+    local = gpu.read(out, (world * rows, H // world, D)).copy()
+    hs = slice(rank * plan.local_heads, (rank + 1) * plan.local_heads)
+    want, _ = oracle.attention(full[0][None, :L, hs], full[1][None, :L, hs], full[2][None, :L, hs], scale)
+    err_max = np.abs(oracle.from_bf16(local[:L]) - want[0]).max()
+    assert err_max <= 1e-2, err_max
+    gpu.call("ulysses_gather_heads_bf16", comm, out, scratch, rows, H, D)
+    gathered = gpu.read(out, (rows, H, D))
+    # every rank's heads of my rows: recompute with the oracle on my valid rows
+    mine = slice(rank * rows, min(L, (rank + 1) * rows))
+    n = mine.stop - mine.start
+    if n > 0:
+        want_rows, _ = oracle.attention(full[0][None, mine], full[1][None, :L], full[2][None, :L], scale)
+        assert np.abs(oracle.from_bf16(gathered[:n]) - want_rows[0]).max() <= 1e-2
+    # all-gather of a row shard
+    total = gpu.empty_bf16(world * rows * H * D)
+    src = gpu.tensor(shards[0][rank])
+    gpu.call("all_gather_bf16", comm, total, src, rows * H * D)
+    assert np.array_equal(gpu.read(total, (world, rows, H, D)), shards[0])
+    assert gpu.device_status() == 0
+    lib.h3_gpu_comm_free(comm)
+    gpu.close()
+    print("OK rank %d" % rank, flush=True)
+
+
+if __name__ == "__main__":
+    main()
