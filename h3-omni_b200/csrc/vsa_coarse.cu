@@ -7,6 +7,8 @@
 #include <cuda_bf16.h>
 #include <math_constants.h>
 
+#include <cstdio>
+
 #include "attn_kernels.h"
 
 namespace h3b {
@@ -384,3 +386,71 @@ cudaError_t vsa_untile_merge(void *output, const void *tiled, const void *gate,
 }
 
 }  // namespace h3b
+
+// ---- top-k tile selection without any allocation -----------------------------------
+// For callers that may not allocate device memory at the point of the call: code running
+// inside someone else's memory plan (a fixed arena handed out once at start-up), under a
+// memory-capped container where a late allocation can fail, or on a real-time path where
+// the driver's allocator lock is not acceptable. The pooled means of Q and K - the only
+// intermediate the selection needs - live in one file-scope device array instead of buffers
+// owned by an h3_gpu_vsa object.
+namespace h3b {
+namespace {
+constexpr unsigned STATIC_TOPK_MAX_ROWS = 8192;  // heads * tiles
+// [2][heads * tiles][128] f32 = 8 MiB, resident on every GPU that loads the library.
+static __device__ __align__(256) float g_topk_pool[2 * (size_t)STATIC_TOPK_MAX_ROWS * VD];
+thread_local char g_topk_error[160] = "";
+}  // namespace
+}  // namespace h3b
+
+extern "C" const char *h3b_vsa_topk_static_error(void) { return h3b::g_topk_error; }
+
+extern "C" cudaError_t h3b_vsa_topk_static(const void *query, const void *key, const int *map,
+                                           const int *sizes, int *indices, int *counts,
+                                           unsigned tiles, unsigned prefix, unsigned keep,
+                                           unsigned heads, cudaStream_t stream) {
+    using namespace h3b;
+    g_topk_error[0] = 0;
+    if (!query || !key || !map || !sizes || !indices || !counts) {
+        snprintf(g_topk_error, sizeof g_topk_error, "h3b_vsa_topk_static: null pointer argument");
+        return cudaErrorInvalidValue;
+    }
+    if (!tiles || !heads || tiles > 4096u || prefix > tiles || !keep || keep > tiles - prefix) {
+        snprintf(g_topk_error, sizeof g_topk_error,
+                 "h3b_vsa_topk_static: bad geometry (tiles %u, prefix %u, keep %u, heads %u)", tiles,
+                 prefix, keep, heads);
+        return cudaErrorInvalidValue;
+    }
+    if ((size_t)heads * tiles > STATIC_TOPK_MAX_ROWS) {
+        snprintf(g_topk_error, sizeof g_topk_error,
+                 "h3b_vsa_topk_static: heads * tiles = %zu exceeds the static scratch limit of %u",
+                 (size_t)heads * tiles, STATIC_TOPK_MAX_ROWS);
+        return cudaErrorInvalidValue;
+    }
+    // Device address of the scratch array, resolved once per device with that device current.
+    // (In host code the array's name is only a handle for the runtime, not an address.)
+    static float *pool_of_device[64] = {};
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    float *pool = __atomic_load_n(&pool_of_device[device], __ATOMIC_ACQUIRE);
+    if (!pool) {
+        e = cudaGetSymbolAddress(reinterpret_cast<void **>(&pool), g_topk_pool);
+        if (e != cudaSuccess) {
+            snprintf(g_topk_error, sizeof g_topk_error, "h3b_vsa_topk_static: %s",
+                     cudaGetErrorString(e));
+            return e;
+        }
+        __atomic_store_n(&pool_of_device[device], pool, __ATOMIC_RELEASE);
+    }
+    float *poolq = pool, *poolk = pool + (size_t)STATIC_TOPK_MAX_ROWS * VD;
+    const void *src[3] = {query, key, nullptr};
+    void *no_tiled[3] = {nullptr, nullptr, nullptr};
+    float *pooled[3] = {poolq, poolk, nullptr};
+    e = vsa_tile_pool3(src, no_tiled, pooled, map, sizes, (int)tiles, (int)heads, 2, stream);
+    if (e != cudaSuccess) return e;
+    return vsa_score_select_compress(poolq, poolk, nullptr, nullptr, indices, counts, nullptr,
+                                     (int)tiles, (int)prefix, (int)keep, (int)heads,
+                                     1.0f / sqrtf(128.0f), stream);
+}

@@ -189,6 +189,31 @@ int h3b_vsa_set_keep(h3_gpu_vsa *vsa, int keep);
 int h3b_vsa_trace_scores(h3_gpu_vsa *vsa, int enable);
 void *h3b_vsa_buffer(const h3_gpu_vsa *vsa, int which);
 
+/* Top-k tile selection of video sparse attention with no device allocation at all. It has no
+ * counterpart in the reference: it is for callers that cannot allocate where they call from -
+ * a host that gave this code a fixed memory arena at start-up, a memory-capped deployment
+ * where a late cudaMalloc may fail, or a latency-critical loop that must not take the
+ * allocator's lock. It computes the pooled means of query and key per tile and from them
+ * indices [heads][tiles][tiles] and counts [heads][tiles], exactly as h3_gpu_vsa_bf16 does
+ * internally, but keeps the pooled means in one 8 MiB device array that is part of the
+ * library image (every GPU that loads the library holds it until the process exits).
+ *   - Limit: heads * tiles <= 8192; larger shapes return cudaErrorInvalidValue and
+ *     h3b_vsa_topk_static_error() says why. Nothing is launched in that case.
+ *   - query, key: [rows][heads][128] bf16; map [tiles*64] and sizes [tiles] as built by
+ *     h3_gpu_vsa_new (device pointers); indices and counts are written in full.
+ *   - The first call on each device resolves the array's device address (a runtime query,
+ *     no allocation); make that first call before starting any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents. Every call
+ *     rewrites the part it reads, so nothing needs clearing, but two calls whose kernels can
+ *     overlap on the GPU (different streams, or different host threads) race on it: keep
+ *     calls on one device ordered.
+ * It calls no cudaMalloc, cudaFree or any allocating library routine. */
+cudaError_t h3b_vsa_topk_static(const void *query, const void *key, const int *map,
+                                const int *sizes, int *indices, int *counts, unsigned tiles,
+                                unsigned prefix, unsigned keep, unsigned heads,
+                                cudaStream_t stream);
+const char *h3b_vsa_topk_static_error(void);
+
 #ifdef __cplusplus
 }
 #endif
