@@ -52,7 +52,9 @@ def build(force=False, verbose=False):
 
     with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
         objects = list(pool.map(compile_one, SOURCES))
-    link = [nvcc(), "-shared", "-o", str(LIB), *objects, "-lnccl", "-lcudart"]
+    # -Bsymbolic: calls between this library's own exported functions never bind to another
+    # library that exports the same reference ABI names in the same process.
+    link = [nvcc(), "-shared", "-o", str(LIB), *objects, "-lnccl", "-lcudart", "-Xlinker", "-Bsymbolic"]
     r = subprocess.run(link, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n" + r.stderr)
