@@ -6,16 +6,17 @@
  * the test-suite, the smoke check and the CPU-baseline leg of the benchmark
  * may load it. Nothing the library ships calls into it.
  *
- * The reference has no CPU attention path and ships no golden tensors for
- * attention (its tests hold error thresholds only), and its dense kernels
- * live in un-vendored third-party trees (FlashAttention 979702c / v2.8.3
- * 060c918, ThunderKittens 6c27e28). Bit-level parity with those kernels is
- * therefore UNPINNED; what is pinned is
- *   - the reference's own acceptance thresholds (tests/pytorch/acceptance.json:5-8,
- *     tests/live/attention.py:38, tests/fasth3/vsa.py:131), and
- *   - bit-exact agreement of the VSA coarse stage, Ulysses index algebra and
- *     FP32 fallback attention with the reference's own CUDA code where that
- *     code still runs on the GPU box (see oracle/ref_build.sh).
+ * The reference has no CPU attention path. Pins of this restatement:
+ *   - golden outputs of the reference's own CUDA code (FP32 fallback attention, tile pooling,
+ *     cuBLAS pooled scores + softmax, block selection, compression), produced on a B200 by
+ *     tests/golden/make_reference_fixtures.py and checked on CPU by tests/test_golden.py;
+ *   - the same reference code run live on the GPU box (oracle/ref_build.py,
+ *     tests/test_reference_backend.py).
+ * The reference's dense and fine-stage kernels live in un-vendored third-party trees
+ * (FlashAttention 979702c / v2.8.3 060c918, ThunderKittens 6c27e28) and are sm_90a-only:
+ * bit-level parity with THOSE kernels is unpinned; for them the reference's own acceptance
+ * thresholds apply (tests/pytorch/acceptance.json:5-8, tests/live/attention.py:38,
+ * tests/fasth3/vsa.py:131).
  *
  * Each function cites the reference file:line it follows.
  */
