@@ -30,9 +30,10 @@ import __graft_entry__ as entry  # noqa: E402
 SEQ_VIDEO, SEQ_AUDIO, HEADS, DIM = 51840, 512, 24, 128
 SEQ = SEQ_VIDEO + SEQ_AUDIO
 SCALE = float(1.0 / np.sqrt(128.0))
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dense kernel at the full
-# workload, scaled from the ncu capture summarised in profiles/ (None until captured).
-DENSE_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dense kernel: the ncu capture
+# summarised in profiles/ measured 384.8 MB at L=16,384, H=24 (algorithmic 402.7 MB; part of the
+# output was still in L2 at kernel end); traffic grows with L*H, so per row of one head:
+DENSE_TRAFFIC_BYTES_PER_ROW_HEAD = 384.8e6 / (16384 * 24)
 
 
 def peaks():
@@ -309,7 +310,8 @@ def main():
                      "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
                      "peak_source": pk["source"] + " burst", "frac_of_sustained": achieved / pk["tflops_sustained"],
                      "frac_of_nominal_2250": achieved / 2250.0, "kernel_ms": kernel_ms,
-                     "flops_per_launch": kernel_flops, "traffic": DENSE_TRAFFIC_BYTES},
+                     "flops_per_launch": kernel_flops,
+                     "traffic": DENSE_TRAFFIC_BYTES_PER_ROW_HEAD * SEQ * HEADS / world},
         "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": 3 * shard_elems * 2, "d2h_bytes_per_step": shard_elems * 2},
         "gpu_launches": counted,

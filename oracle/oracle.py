@@ -33,7 +33,16 @@ def lib():
 
 
 def _p(a):
-    return None if a is None else a.ctypes.data_as(C.c_void_p)
+    """Pointer to a C-contiguous array (the C side indexes raw memory)."""
+    if a is None:
+        return None
+    if not a.flags["C_CONTIGUOUS"]:
+        raise ValueError("oracle arrays must be C-contiguous")
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _c(*arrays):
+    return [np.ascontiguousarray(a) for a in arrays]
 
 
 def to_bf16(x):
@@ -65,6 +74,7 @@ def normal_bf16(shape, seed, sigma=1.0):
 
 def attention(q, k, v, scale, causal=False, elem="bf16", want_lse=False):
     """q: [B, Lq, H, D], k/v: [B, Lk, KH, D] uint16. Returns (out_f32, out_16[, lse])."""
+    q, k, v = _c(q, k, v)
     b, lq, h, d = q.shape
     lk, kh = k.shape[1], k.shape[2]
     out32 = np.empty(q.shape, dtype=np.float32)
@@ -77,6 +87,7 @@ def attention(q, k, v, scale, causal=False, elem="bf16", want_lse=False):
 
 def attention_rows_f64(rows, q, k, v, scale):
     """q: [Lq, H, D]; rows: int array. Returns [len(rows), H, D] f32 (FP64 accumulation)."""
+    q, k, v = _c(q, k, v)
     lq, h, d = q.shape
     lk, kh = k.shape[0], k.shape[1]
     rows = np.ascontiguousarray(rows, dtype=np.int32)
@@ -102,6 +113,7 @@ class VsaMap:
 
 
 def vsa_tile_pool(src, vmap, want_tiled=True):
+    src, = _c(src)
     rows, heads, d = src.shape
     tiled = np.empty((heads, vmap.tiles * 64, d), dtype=np.uint16) if want_tiled else None
     pooled = np.empty((heads, vmap.tiles, d), dtype=np.float32)
@@ -111,6 +123,7 @@ def vsa_tile_pool(src, vmap, want_tiled=True):
 
 
 def vsa_scores(poolq, poolk, scale):
+    poolq, poolk = _c(poolq, poolk)
     heads, tiles, _ = poolq.shape
     scores = np.empty((heads, tiles, tiles), dtype=np.float32)
     lib().oracle_vsa_scores(_p(scores), _p(poolq), _p(poolk), tiles, heads, C.c_float(scale))
@@ -118,6 +131,7 @@ def vsa_scores(poolq, poolk, scale):
 
 
 def vsa_select(scores, prefix, keep):
+    scores, = _c(scores)
     heads, tiles, _ = scores.shape
     indices = np.full((heads, tiles, tiles), -1, dtype=np.int32)
     counts = np.empty((heads, tiles), dtype=np.int32)
@@ -126,6 +140,7 @@ def vsa_select(scores, prefix, keep):
 
 
 def vsa_fine(q, k, v, indices, counts, sizes, round_p=True):
+    q, k, v, indices, counts, sizes = _c(q, k, v, indices, counts, sizes)
     heads, padded, d = q.shape
     tiles = padded // 64
     out = np.empty(q.shape, dtype=np.uint16)
@@ -144,6 +159,7 @@ def vsa_pooled_softmax(scores):
 
 
 def vsa_compress(prob, poolv):
+    prob, poolv = _c(prob, poolv)
     heads, tiles, d = poolv.shape
     out = np.empty((heads, tiles, d), dtype=np.float32)
     lib().oracle_vsa_compress(_p(out), _p(prob), _p(poolv), tiles, heads)
@@ -151,6 +167,7 @@ def vsa_compress(prob, poolv):
 
 
 def vsa_untile_merge(tiled, gate, compression, vmap, out=None):
+    tiled, gate, compression = _c(tiled, gate, compression)
     rows, heads, d = gate.shape
     if out is None:
         out = np.zeros((rows, heads, d), dtype=np.uint16)
@@ -193,6 +210,7 @@ def ulysses(x, inverse=False):
 
 def time_attention(q, k, v, scale):
     """Seconds for one bf16 dense attention pass on all OpenMP threads. q: [Lq,H,D]."""
+    q, k, v = _c(q, k, v)
     lq, h, d = q.shape
     out = np.empty(q.shape, dtype=np.uint16)
     return lib().oracle_time_attention(_p(out), _p(q), _p(k), _p(v), lq, k.shape[0], h, d,
