@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+struct CUtensorMap_st;
+
 namespace h3b {
 
 // Address of this device's status word (0 = ok; see DeviceStatus in sm100_ptx.cuh).
@@ -12,6 +14,11 @@ cudaError_t device_status_word(int **word);
 cudaError_t attn_dense_tc5(void *out, const void *q, const void *k, const void *v, float *lse,
                            unsigned batch, unsigned lq, unsigned lk, unsigned heads,
                            unsigned kv_heads, float scale, cudaStream_t stream);
+// Two query tiles per CTA (attn_tc5_pair.cu); tensor maps as built by attn_dense_tc5.
+cudaError_t attn_dense_tc5_pair(const ::CUtensorMap_st *mq, const ::CUtensorMap_st *mk,
+                                const ::CUtensorMap_st *mv, void *out, float *lse, unsigned batch,
+                                unsigned lq, unsigned lk, unsigned heads, unsigned kv_heads,
+                                float scale, int *status, cudaStream_t stream);
 // Head-major tiled [H][tiles*64][128] bf16 with per-(head, query tile) KV tile lists.
 cudaError_t attn_sparse_tc5(void *out, const void *q, const void *k, const void *v, float *lse,
                             const int *indices, const int *counts, const int *sizes,

@@ -21,6 +21,7 @@
 
 #include "attn_kernels.h"
 #include "sm100_ptx.cuh"
+#include "softmax_tc5.cuh"
 
 namespace h3b {
 
@@ -52,128 +53,6 @@ struct Tc5Config {
     static constexpr int HALF_BYTES = BN * 128;    // one 64-column half of a tile
     static constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * TILE_BYTES + 1024;
 };
-
-// ---- softmax building blocks: one thread owns one query row of S in TMEM ----------
-__device__ __forceinline__ float max3(float a, float b, float c) {
-    float d;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
-__device__ __forceinline__ void max_chunk(const uint32_t (&v)[32], float &m0, float &m1) {
-#pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-        m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-        m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-    }
-}
-// Row maximum over a full tile. Loads of the next 32 columns are in flight while the
-// current 32 are reduced.
-template <int BN>
-__device__ __forceinline__ float row_max_full(uint32_t s_addr) {
-    constexpr int NC = BN / 32;
-    uint32_t a[32], b[32];
-    float m0 = -INFINITY, m1 = -INFINITY;
-    tmem_ld32(s_addr, a);
-    tmem_wait_ld();
-#pragma unroll
-    for (int c = 0; c < NC; c += 2) {
-        if (c + 1 < NC) tmem_ld32(s_addr + (c + 1) * 32, b);
-        max_chunk(a, m0, m1);
-        if (c + 1 < NC) {
-            tmem_wait_ld();
-            if (c + 2 < NC) tmem_ld32(s_addr + (c + 2) * 32, a);
-            max_chunk(b, m0, m1);
-            if (c + 2 < NC) tmem_wait_ld();
-        }
-    }
-    return fmaxf(m0, m1);
-}
-template <int BN>
-__device__ __forceinline__ float row_max_masked(uint32_t s_addr, int nvalid) {
-    float mx = -INFINITY;
-#pragma unroll
-    for (int c = 0; c < BN / 32; c++) {
-        uint32_t v[32];
-        tmem_ld32(s_addr + c * 32, v);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; i++)
-            if (c * 32 + i < nvalid) mx = fmaxf(mx, __uint_as_float(v[i]));
-    }
-    return mx;
-}
-// p = exp2(s * scale_log2 + neg) for 32 columns, packed pairwise to bf16; partial row sums
-// accumulate in two float2 chains (packed f32x2 arithmetic halves the FMA-pipe work).
-__device__ __forceinline__ void exp_chunk(const uint32_t (&v)[32], uint32_t (&packed)[16],
-                                          float2 scale2, float2 neg2, float2 &sum0, float2 &sum1) {
-#pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-        const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])),
-                                     scale2, neg2);
-        const float2 x1 = __ffma2_rn(
-            make_float2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])), scale2, neg2);
-        const float2 p0 = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
-        const float2 p1 = make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
-        sum0 = __fadd2_rn(sum0, p0);
-        sum1 = __fadd2_rn(sum1, p1);
-        packed[i / 2] = pack_bf16(p0.x, p0.y);
-        packed[i / 2 + 1] = pack_bf16(p1.x, p1.y);
-    }
-}
-// Full tile: P overwrites S in place (bf16 pairs, half the columns), loads one chunk ahead.
-template <int BN>
-__device__ __forceinline__ float exp_store_full(uint32_t s_addr, float scale_log2, float neg) {
-    constexpr int NC = BN / 32;
-    uint32_t a[32], b[32], packed[16];
-    float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
-    const float2 scale2 = make_float2(scale_log2, scale_log2), neg2 = make_float2(neg, neg);
-    tmem_ld32(s_addr, a);
-    tmem_wait_ld();
-#pragma unroll
-    for (int c = 0; c < NC; c += 2) {
-        if (c + 1 < NC) tmem_ld32(s_addr + (c + 1) * 32, b);
-        exp_chunk(a, packed, scale2, neg2, sum0, sum1);
-        tmem_st16(s_addr + c * 16, packed);
-        if (c + 1 < NC) {
-            tmem_wait_ld();
-            if (c + 2 < NC) tmem_ld32(s_addr + (c + 2) * 32, a);
-            exp_chunk(b, packed, scale2, neg2, sum0, sum1);
-            tmem_st16(s_addr + (c + 1) * 16, packed);
-            if (c + 2 < NC) tmem_wait_ld();
-        }
-    }
-    return (sum0.x + sum0.y) + (sum1.x + sum1.y);
-}
-template <int BN>
-__device__ __forceinline__ float exp_store_masked(uint32_t s_addr, float scale_log2, float neg,
-                                                  int nvalid) {
-    float sum = 0.0f;
-#pragma unroll
-    for (int c = 0; c < BN / 32; c++) {
-        uint32_t v[32], packed[16];
-        tmem_ld32(s_addr + c * 32, v);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-            float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), scale_log2, neg));
-            float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), scale_log2, neg));
-            if (c * 32 + i >= nvalid) p0 = 0.0f;
-            if (c * 32 + i + 1 >= nvalid) p1 = 0.0f;
-            sum += p0 + p1;
-            packed[i / 2] = pack_bf16(p0, p1);
-        }
-        tmem_st16(s_addr + c * 16, packed);
-    }
-    return sum;
-}
-template <int BN>
-__device__ __forceinline__ void store_zero_p(uint32_t s_addr) {
-    uint32_t zero[16];
-#pragma unroll
-    for (int i = 0; i < 16; i++) zero[i] = 0u;
-#pragma unroll
-    for (int c = 0; c < BN / 32; c++) tmem_st16(s_addr + c * 16, zero);
-}
 
 template <int BN, bool SPARSE>
 __global__ void __launch_bounds__(TC5_THREADS, 2)
@@ -603,6 +482,10 @@ cudaError_t attn_dense_tc5(void *out, const void *q, const void *k, const void *
     p.out = static_cast<__nv_bfloat16 *>(out);
     p.lse = lse;
     p.status = status;
+    // More than one query tile: the two-tile-per-CTA kernel (attn_tc5_pair.cu).
+    if (lq > (unsigned)BM)
+        return attn_dense_tc5_pair(&mq, &mk, &mv, out, lse, batch, lq, lk, heads, kv_heads, scale,
+                                   status, stream);
     dim3 grid((lq + BM - 1) / BM, heads, batch);
     return launch<128, false>(mq, mk, mv, p, grid, stream);
 }

@@ -1,0 +1,363 @@
+// Dense attention forward, two query tiles per CTA (tcgen05 + TMEM + TMA), bf16, head dim 128.
+//
+// The single-tile kernel in attn_tc5.cu relies on two co-resident CTAs to overlap softmax
+// with MMAs, but nothing keeps the two CTAs out of phase, and each loads K/V for itself.
+// Here one CTA owns 256 query rows as two 128-row tiles A and B that share every K/V tile,
+// and the MMA warp enforces the interleaving
+//      PV_A(j)  QK_A(j+1)  PV_B(j)  QK_B(j+1)  ...
+// so that while softmax warpgroup A works on S_A(j+1) the tensor pipe runs B's MMAs and vice
+// versa. One CTA per SM: all 512 TMEM columns (S_A, S_B, O_A, O_B, 128 each), 64 KB of Q and a
+// four-stage K/V ring in shared memory.
+//   warps 0-3 / 4-7 : softmax warpgroups A / B (one thread per query row, the row's 128
+//                     scores held in registers: one TMEM read pass)
+//   warp 8          : TMA producer
+//   warp 9          : MMA issuer      (warps 8-11 give most of their registers to the
+//                                      softmax warpgroups with setmaxnreg)
+// A fixed fraction of the exponentials is evaluated by a polynomial on the FMA pipe (see
+// softmax_tc5.cuh) so the exponential unit is not the critical resource.
+// Serves h3_flash3_bf16 / h3_flash3_cross_bf16 / non-causal h3_flash_bf16 whenever the call
+// has more than one query tile (replacing the reference's cuda/flash3_attention.cu:18-94).
+#include <cuda.h>
+
+#include "attn_kernels.h"
+#include "softmax_tc5.cuh"
+
+namespace h3b {
+namespace {
+
+constexpr int PBM = 128, PBN = 128, PHD = 128;
+constexpr int PAIR_THREADS = 384;                  // three warpgroups: softmax A, softmax B, {TMA, MMA}
+constexpr int PAIR_STAGES = 4;                      // K0 V0 K1 V1 ... ring of 32 KB tiles
+constexpr int PAIR_TILE_BYTES = PBN * PHD * 2;      // 32 KB
+constexpr int PAIR_HALF_BYTES = PBN * 128;          // one 64-column half
+constexpr int PAIR_Q_BYTES = 2 * PBM * PHD * 2;     // 64 KB
+constexpr int PAIR_SMEM_BYTES = PAIR_Q_BYTES + PAIR_STAGES * PAIR_TILE_BYTES + 1024;
+constexpr int PAIR_O_COL = 256;
+constexpr float PAIR_RESCALE_LOG2 = 8.0f;
+constexpr int PAIR_POLY_EVERY = 2;                  // 25 % of the exponentials on the FMA pipe
+
+struct PairParams {
+    int lq, lk, heads, kv_heads;
+    float scale, scale_log2;
+    __nv_bfloat16 *out;
+    float *lse;
+    int *status;
+};
+
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const PairParams p) {
+    constexpr int ST = PAIR_STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bars[1 + 2 * ST + 6];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_word;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_smem = smem_base;
+    const uint32_t ring = q_smem + PAIR_Q_BYTES;
+
+    const uint32_t bar0 = smem_u32(bars);
+    const uint32_t bar_q_full = bar0;
+    auto bar_full = [&](int s) { return bar0 + 8u * (1 + s); };
+    auto bar_empty = [&](int s) { return bar0 + 8u * (1 + ST + s); };
+    auto bar_s_full = [&](int t) { return bar0 + 8u * (1 + 2 * ST + t); };
+    auto bar_p_full = [&](int t) { return bar0 + 8u * (1 + 2 * ST + 2 + t); };
+    auto bar_pv_done = [&](int t) { return bar0 + 8u * (1 + 2 * ST + 4 + t); };
+
+    const int head = blockIdx.y, batch = blockIdx.z;
+    const int kv_head = head / (p.heads / p.kv_heads);
+    const int q_row0 = blockIdx.x * 2 * PBM;
+    const int n_tiles = (p.lk + PBN - 1) / PBN;
+
+    if (tid == 0) {
+        mbar_init(bar_q_full, 1);
+        for (int s = 0; s < ST; s++) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int t = 0; t < 2; t++) {
+            mbar_init(bar_s_full(t), 1);
+            mbar_init(bar_p_full(t), 128);
+            mbar_init(bar_pv_done(t), 1);
+        }
+        mbar_fence_init();
+        abort_word = 0;
+    }
+    if (warp == 9) {
+        tmem_alloc(smem_u32(&tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc5_fence_before();
+    __syncthreads();
+    tc5_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp >= 8) {
+    warpgroup_reg_dec<56>();
+    if (warp == 8) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&map_q);
+            tma_prefetch_desc(&map_k);
+            tma_prefetch_desc(&map_v);
+            mbar_arrive_expect_tx(bar_q_full, PAIR_Q_BYTES);
+            for (int t = 0; t < 2; t++) {
+                const uint32_t dst = q_smem + t * (PAIR_Q_BYTES / 2);
+                tma_load_4d(dst, &map_q, bar_q_full, 0, head, q_row0 + t * PBM, batch);
+                tma_load_4d(dst + PAIR_HALF_BYTES, &map_q, bar_q_full, 64, head, q_row0 + t * PBM, batch);
+            }
+            for (int idx = 0; idx < 2 * n_tiles; idx++) {   // even: K tile idx/2, odd: V tile idx/2
+                const int s = idx % ST, use = idx / ST;
+                if (use > 0 && !mbar_wait(bar_empty(s), (use - 1) & 1, &abort_word)) break;
+                const uint32_t dst = ring + s * PAIR_TILE_BYTES;
+                const void *map = (idx & 1) ? (const void *)&map_v : (const void *)&map_k;
+                mbar_arrive_expect_tx(bar_full(s), PAIR_TILE_BYTES);
+                tma_load_4d(dst, map, bar_full(s), 0, kv_head, (idx / 2) * PBN, batch);
+                tma_load_4d(dst + PAIR_HALF_BYTES, map, bar_full(s), 64, kv_head, (idx / 2) * PBN, batch);
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------- MMA issuer -------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = mma_idesc(PBM, PBN, 1, 0);
+            constexpr uint32_t idesc_pv = mma_idesc(PBM, PHD, 1, 1);
+            auto wait_stage = [&](int idx) {
+                return mbar_wait(bar_full(idx % ST), (idx / ST) & 1, &abort_word);
+            };
+            auto issue_qk = [&](int j, int t) {   // S_t = Q_t . K_j^T
+                const uint32_t kd = ring + ((2 * j) % ST) * PAIR_TILE_BYTES;
+                const uint32_t qd = q_smem + t * (PAIR_Q_BYTES / 2);
+#pragma unroll
+                for (int kk = 0; kk < PHD / 16; kk++) {
+                    const uint64_t a =
+                        smem_desc_sw128(qd + (kk / 4) * PAIR_HALF_BYTES + (kk % 4) * 32, 16, 1024);
+                    const uint64_t b =
+                        smem_desc_sw128(kd + (kk / 4) * PAIR_HALF_BYTES + (kk % 4) * 32, 16, 1024);
+                    mma_ss(tmem + t * PBN, a, b, idesc_qk, kk > 0);
+                }
+                mma_commit(bar_s_full(t));
+            };
+            auto issue_pv = [&](int j, int t) {   // O_t += P_t . V_j
+                const uint32_t vd = ring + ((2 * j + 1) % ST) * PAIR_TILE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < PBN / 16; kk++) {
+                    const uint64_t b = smem_desc_sw128(vd + kk * 2048, PAIR_HALF_BYTES, 1024);
+                    mma_ts(tmem + PAIR_O_COL + t * PHD, tmem + t * PBN + kk * 8, b, idesc_pv,
+                           (j > 0) || (kk > 0));
+                }
+                mma_commit(bar_pv_done(t));
+            };
+            bool alive = mbar_wait(bar_q_full, 0, &abort_word) && wait_stage(0);
+            if (alive) {
+                tc5_fence_after();
+                issue_qk(0, 0);
+                issue_qk(0, 1);
+                mma_commit(bar_empty(0));
+            }
+            for (int j = 0; alive && j < n_tiles; j++) {
+                const bool more = j + 1 < n_tiles;
+                if (!mbar_wait(bar_p_full(0), j & 1, &abort_word) || !wait_stage(2 * j + 1)) break;
+                tc5_fence_after();
+                issue_pv(j, 0);
+                if (more) {
+                    if (!wait_stage(2 * j + 2)) break;
+                    tc5_fence_after();
+                    issue_qk(j + 1, 0);
+                }
+                if (!mbar_wait(bar_p_full(1), j & 1, &abort_word)) break;
+                tc5_fence_after();
+                issue_pv(j, 1);
+                mma_commit(bar_empty((2 * j + 1) % ST));
+                if (more) {
+                    issue_qk(j + 1, 1);
+                    mma_commit(bar_empty((2 * j + 2) % ST));
+                }
+            }
+        }
+    }
+    } else {
+        warpgroup_reg_inc<224>();
+        // ------------------------------ online softmax ------------------------------
+        const int t = warp >> 2;                // which query tile
+        const int r = tid & 127;                // row inside the tile == TMEM lane
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t s_addr = tmem + lane_base + t * PBN;
+        const uint32_t o_addr = tmem + lane_base + PAIR_O_COL + t * PHD;
+        float m_ref = -INFINITY, l = 0.0f;
+        bool alive = true;
+        for (int j = 0; j < n_tiles; j++) {
+            const int nvalid = min(PBN, p.lk - j * PBN);
+            alive = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), j & 1, &abort_word));
+            if (!alive) break;
+            tc5_fence_after();
+            bool saw_prev_pv = (j == 0);
+            if (nvalid >= PBN) {
+                // the whole row of scores in registers: one TMEM read pass
+                uint32_t s0[32], s1[32], s2[32], s3[32];
+                tmem_ld32(s_addr, s0);
+                tmem_ld32(s_addr + 32, s1);
+                tmem_ld32(s_addr + 64, s2);
+                tmem_ld32(s_addr + 96, s3);
+                tmem_wait_ld();
+                float ma = -INFINITY, mb = -INFINITY;
+                max_chunk(s0, ma, mb);
+                max_chunk(s1, ma, mb);
+                max_chunk(s2, ma, mb);
+                max_chunk(s3, ma, mb);
+                const float m_new = fmaxf(m_ref, fmaxf(ma, mb));
+                const bool grow = (m_new - m_ref) * p.scale_log2 > PAIR_RESCALE_LOG2;
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float alpha = grow ? fast_exp2((m_ref - m_new) * p.scale_log2) : 1.0f;
+                    if (grow) m_ref = m_new;
+                    l *= alpha;
+                    if (j > 0) {
+                        alive = __all_sync(0xffffffffu,
+                                           mbar_wait(bar_pv_done(t), (j - 1) & 1, &abort_word));
+                        if (!alive) break;
+                        saw_prev_pv = true;
+                        tc5_fence_after();
+#pragma unroll
+                        for (int c = 0; c < PHD / 32; c++) {
+                            uint32_t v[32];
+                            tmem_ld32(o_addr + c * 32, v);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; i++)
+                                v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                            tmem_st32(o_addr + c * 32, v);
+                        }
+                        tmem_wait_st();
+                    }
+                }
+                const float neg = -m_ref * p.scale_log2;
+                const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+                const float2 neg2 = make_float2(neg, neg);
+                float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
+                uint32_t packed[16];
+                exp_chunk_mixed<PAIR_POLY_EVERY>(s0, packed, scale2, neg2, sum0, sum1);
+                tmem_st16(s_addr, packed);
+                exp_chunk_mixed<PAIR_POLY_EVERY>(s1, packed, scale2, neg2, sum0, sum1);
+                tmem_st16(s_addr + 16, packed);
+                exp_chunk_mixed<PAIR_POLY_EVERY>(s2, packed, scale2, neg2, sum0, sum1);
+                tmem_st16(s_addr + 32, packed);
+                exp_chunk_mixed<PAIR_POLY_EVERY>(s3, packed, scale2, neg2, sum0, sum1);
+                tmem_st16(s_addr + 48, packed);
+                l += (sum0.x + sum0.y) + (sum1.x + sum1.y);
+            } else {
+                // ragged last tile: masked two-pass path
+                const float mx = row_max_masked<PBN>(s_addr, nvalid);
+                const float m_new = fmaxf(m_ref, mx);
+                const bool grow = (m_new - m_ref) * p.scale_log2 > PAIR_RESCALE_LOG2;
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float alpha = grow ? fast_exp2((m_ref - m_new) * p.scale_log2) : 1.0f;
+                    if (grow) m_ref = m_new;
+                    l *= alpha;
+                    if (j > 0) {
+                        alive = __all_sync(0xffffffffu,
+                                           mbar_wait(bar_pv_done(t), (j - 1) & 1, &abort_word));
+                        if (!alive) break;
+                        saw_prev_pv = true;
+                        tc5_fence_after();
+#pragma unroll
+                        for (int c = 0; c < PHD / 32; c++) {
+                            uint32_t v[32];
+                            tmem_ld32(o_addr + c * 32, v);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; i++)
+                                v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                            tmem_st32(o_addr + c * 32, v);
+                        }
+                        tmem_wait_st();
+                    }
+                }
+                l += exp_store_masked<PBN>(s_addr, p.scale_log2, -m_ref * p.scale_log2, nvalid);
+            }
+            if (!saw_prev_pv) {
+                alive = __all_sync(0xffffffffu, mbar_wait(bar_pv_done(t), (j - 1) & 1, &abort_word));
+                if (!alive) break;
+            }
+            tmem_wait_st();
+            tc5_fence_before();
+            mbar_arrive(bar_p_full(t));
+        }
+
+        // -------- epilogue: O / l -> bf16, straight to global memory --------
+        if (alive) alive = __all_sync(0xffffffffu, mbar_wait(bar_pv_done(t), (n_tiles - 1) & 1, &abort_word));
+        if (alive) {
+            tc5_fence_after();
+            const float inv = 1.0f / l;
+            const int row = q_row0 + t * PBM + r;
+            const bool store = row < p.lq;
+            __nv_bfloat16 *dst = p.out + (((size_t)batch * p.lq + row) * p.heads + head) * PHD;
+            if (store && p.lse)
+                p.lse[((size_t)batch * p.heads + head) * p.lq + row] = m_ref * p.scale + __logf(l);
+#pragma unroll
+            for (int c = 0; c < PHD / 32; c++) {
+                uint32_t v[32];
+                tmem_ld32(o_addr + c * 32, v);
+                tmem_wait_ld();
+                if (store) {
+                    uint4 *d4 = reinterpret_cast<uint4 *>(dst + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(v[i * 8 + 0]) * inv, __uint_as_float(v[i * 8 + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(v[i * 8 + 2]) * inv, __uint_as_float(v[i * 8 + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(v[i * 8 + 4]) * inv, __uint_as_float(v[i * 8 + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(v[i * 8 + 6]) * inv, __uint_as_float(v[i * 8 + 7]) * inv);
+                        d4[i] = w;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------- teardown ----------------------------------
+    tc5_fence_before();
+    __syncthreads();
+    if (abort_word) {
+        if (tid == 0) atomicCAS(p.status, STATUS_OK, STATUS_WAIT_TIMEOUT);
+        if (warp == 8) __nanosleep(1000000);   // let copies in flight land before smem is reused
+        __syncthreads();
+    }
+    if (warp == 9) {
+        tc5_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+}  // namespace
+
+cudaError_t attn_dense_tc5_pair(const CUtensorMap_st *mq, const CUtensorMap_st *mk,
+                                const CUtensorMap_st *mv, void *out, float *lse, unsigned batch,
+                                unsigned lq, unsigned lk, unsigned heads, unsigned kv_heads,
+                                float scale, int *status, cudaStream_t stream) {
+    static thread_local int configured_device = -1;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (configured_device != device) {
+        e = cudaFuncSetAttribute(attn_tc5_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PAIR_SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        configured_device = device;
+    }
+    PairParams p{};
+    p.lq = (int)lq;
+    p.lk = (int)lk;
+    p.heads = (int)heads;
+    p.kv_heads = (int)kv_heads;
+    p.scale = scale;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.out = static_cast<__nv_bfloat16 *>(out);
+    p.lse = lse;
+    p.status = status;
+    dim3 grid((lq + 2 * PBM - 1) / (2 * PBM), heads, batch);
+    attn_tc5_pair_kernel<<<grid, PAIR_THREADS, PAIR_SMEM_BYTES, stream>>>(*mq, *mk, *mv, p);
+    return cudaGetLastError();
+}
+
+}  // namespace h3b

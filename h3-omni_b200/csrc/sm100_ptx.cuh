@@ -200,6 +200,16 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
                  : "memory");
 }
 
+// Register re-allocation between warpgroups (four aligned warps execute it together).
+template <int REGS>
+__device__ __forceinline__ void warpgroup_reg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
+}
+template <int REGS>
+__device__ __forceinline__ void warpgroup_reg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&v);
