@@ -36,6 +36,16 @@ constexpr int PAIR_O_COL = 256;
 constexpr float PAIR_RESCALE_LOG2 = 8.0f;
 constexpr int PAIR_POLY_EVERY = 2;                  // 25 % of the exponentials on the FMA pipe
 
+#ifdef H3B_TRACE
+// Development aid, compiled only with -DH3B_TRACE: cycle counters of CTA (0,0,0).
+__device__ long long g_pair_trace[32];
+#define TRACE_T0() const long long trace_t0 = clock64()
+#define TRACE_ADD(slot) g_pair_trace_local[slot] += clock64() - trace_t0
+#else
+#define TRACE_T0()
+#define TRACE_ADD(slot)
+#endif
+
 struct PairParams {
     int lq, lk, heads, kv_heads;
     float scale, scale_log2;
@@ -126,29 +136,41 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             auto wait_stage = [&](int idx) {
                 return mbar_wait(bar_full(idx % ST), (idx / ST) & 1, &abort_word);
             };
+            // Descriptors are built once (Q) or once per stage (K, V); a K-step only adds to
+            // the low word: +2 per 32 bytes inside a 64-column half, +1024 for the second half
+            // (16 KB), +128 per 16 V rows (2 KB).
+            uint32_t q_lo[2], q_hi[2];
+            for (int t = 0; t < 2; t++) {
+                const uint64_t d = smem_desc_sw128(q_smem + t * (PAIR_Q_BYTES / 2), 16, 1024);
+                q_lo[t] = (uint32_t)d;
+                q_hi[t] = (uint32_t)(d >> 32);
+            }
+            const uint64_t k_proto = smem_desc_sw128(ring, 16, 1024);
+            const uint64_t v_proto = smem_desc_sw128(ring, PAIR_HALF_BYTES, 1024);
+            const uint32_t k_hi = (uint32_t)(k_proto >> 32), v_hi = (uint32_t)(v_proto >> 32);
+            const uint32_t k_ring_lo = (uint32_t)k_proto, v_ring_lo = (uint32_t)v_proto;  // LBO lives in the low word
             auto issue_qk = [&](int j, int t) {   // S_t = Q_t . K_j^T
-                const uint32_t kd = ring + ((2 * j) % ST) * PAIR_TILE_BYTES;
-                const uint32_t qd = q_smem + t * (PAIR_Q_BYTES / 2);
+                const uint32_t k_lo = k_ring_lo + ((2 * j) % ST) * (PAIR_TILE_BYTES >> 4);
 #pragma unroll
                 for (int kk = 0; kk < PHD / 16; kk++) {
-                    const uint64_t a =
-                        smem_desc_sw128(qd + (kk / 4) * PAIR_HALF_BYTES + (kk % 4) * 32, 16, 1024);
-                    const uint64_t b =
-                        smem_desc_sw128(kd + (kk / 4) * PAIR_HALF_BYTES + (kk % 4) * 32, 16, 1024);
-                    mma_ss(tmem + t * PBN, a, b, idesc_qk, kk > 0);
+                    const uint32_t off = (kk / 4) * (PAIR_HALF_BYTES >> 4) + (kk % 4) * 2;
+                    mma_ss_words(tmem + t * PBN, q_lo[t] + off, q_hi[t], k_lo + off, k_hi, idesc_qk,
+                                 kk > 0);
                 }
                 mma_commit(bar_s_full(t));
             };
             auto issue_pv = [&](int j, int t) {   // O_t += P_t . V_j
-                const uint32_t vd = ring + ((2 * j + 1) % ST) * PAIR_TILE_BYTES;
+                const uint32_t v_lo = v_ring_lo + ((2 * j + 1) % ST) * (PAIR_TILE_BYTES >> 4);
 #pragma unroll
-                for (int kk = 0; kk < PBN / 16; kk++) {
-                    const uint64_t b = smem_desc_sw128(vd + kk * 2048, PAIR_HALF_BYTES, 1024);
-                    mma_ts(tmem + PAIR_O_COL + t * PHD, tmem + t * PBN + kk * 8, b, idesc_pv,
-                           (j > 0) || (kk > 0));
-                }
+                for (int kk = 0; kk < PBN / 16; kk++)
+                    mma_ts_words(tmem + PAIR_O_COL + t * PHD, tmem + t * PBN + kk * 8,
+                                 v_lo + kk * (2048 >> 4), v_hi, idesc_pv, (j > 0) || (kk > 0));
                 mma_commit(bar_pv_done(t));
             };
+#ifdef H3B_TRACE
+            long long g_pair_trace_local[8] = {};
+            const long long trace_begin = clock64();
+#endif
             bool alive = mbar_wait(bar_q_full, 0, &abort_word) && wait_stage(0);
             if (alive) {
                 tc5_fence_after();
@@ -158,15 +180,38 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             }
             for (int j = 0; alive && j < n_tiles; j++) {
                 const bool more = j + 1 < n_tiles;
-                if (!mbar_wait(bar_p_full(0), j & 1, &abort_word) || !wait_stage(2 * j + 1)) break;
-                tc5_fence_after();
-                issue_pv(j, 0);
-                if (more) {
-                    if (!wait_stage(2 * j + 2)) break;
-                    tc5_fence_after();
-                    issue_qk(j + 1, 0);
+                {
+                    TRACE_T0();
+                    if (!mbar_wait(bar_p_full(0), j & 1, &abort_word)) break;
+                    TRACE_ADD(0);
                 }
-                if (!mbar_wait(bar_p_full(1), j & 1, &abort_word)) break;
+                {
+                    TRACE_T0();
+                    if (!wait_stage(2 * j + 1)) break;
+                    TRACE_ADD(1);
+                }
+                tc5_fence_after();
+                {
+                    TRACE_T0();
+                    issue_pv(j, 0);
+                    TRACE_ADD(4);
+                }
+                if (more) {
+                    {
+                        TRACE_T0();
+                        if (!wait_stage(2 * j + 2)) break;
+                        TRACE_ADD(2);
+                    }
+                    tc5_fence_after();
+                    TRACE_T0();
+                    issue_qk(j + 1, 0);
+                    TRACE_ADD(5);
+                }
+                {
+                    TRACE_T0();
+                    if (!mbar_wait(bar_p_full(1), j & 1, &abort_word)) break;
+                    TRACE_ADD(3);
+                }
                 tc5_fence_after();
                 issue_pv(j, 1);
                 mma_commit(bar_empty((2 * j + 1) % ST));
@@ -175,6 +220,18 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     mma_commit(bar_empty((2 * j + 2) % ST));
                 }
             }
+#ifdef H3B_TRACE
+            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+                g_pair_trace[0] = clock64() - trace_begin;   // MMA thread: whole walk
+                g_pair_trace[1] = g_pair_trace_local[0];     // waiting for P of tile A
+                g_pair_trace[2] = g_pair_trace_local[1];     // waiting for V
+                g_pair_trace[3] = g_pair_trace_local[2];     // waiting for K
+                g_pair_trace[4] = g_pair_trace_local[3];     // waiting for P of tile B
+                g_pair_trace[5] = n_tiles;
+                g_pair_trace[6] = g_pair_trace_local[4];     // thread time inside issue_pv(A)
+                g_pair_trace[7] = g_pair_trace_local[5];     // thread time inside issue_qk(A)
+            }
+#endif
         }
     }
     } else {
@@ -187,12 +244,27 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const uint32_t o_addr = tmem + lane_base + PAIR_O_COL + t * PHD;
         float m_ref = -INFINITY, l = 0.0f;
         bool alive = true;
+#ifdef H3B_TRACE
+        long long g_pair_trace_local[8] = {};
+        const long long trace_begin = clock64();
+#endif
         for (int j = 0; j < n_tiles; j++) {
             const int nvalid = min(PBN, p.lk - j * PBN);
-            alive = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), j & 1, &abort_word));
+            {
+                TRACE_T0();
+                alive = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), j & 1, &abort_word));
+                TRACE_ADD(0);
+            }
             if (!alive) break;
             tc5_fence_after();
+#ifdef H3B_TRACE
+            const long long trace_work = clock64();
+#endif
             bool saw_prev_pv = (j == 0);
+#ifdef H3B_SKIP_SOFTMAX
+            if (true) {   // experiment: no softmax work at all, P = whatever S holds
+            } else
+#endif
             if (nvalid >= PBN) {
                 // the whole row of scores in registers: one TMEM read pass
                 uint32_t s0[32], s1[32], s2[32], s3[32];
@@ -282,7 +354,17 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             tmem_wait_st();
             tc5_fence_before();
             mbar_arrive(bar_p_full(t));
+#ifdef H3B_TRACE
+            g_pair_trace_local[1] += clock64() - trace_work;
+#endif
         }
+#ifdef H3B_TRACE
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid & 127) == 0) {
+            g_pair_trace[8 + 4 * t] = clock64() - trace_begin;       // softmax warpgroup t: whole walk
+            g_pair_trace[9 + 4 * t] = g_pair_trace_local[0];         // waiting for S
+            g_pair_trace[10 + 4 * t] = g_pair_trace_local[1];        // S ready -> P delivered
+        }
+#endif
 
         // -------- epilogue: O / l -> bf16, straight to global memory --------
         if (alive) alive = __all_sync(0xffffffffu, mbar_wait(bar_pv_done(t), (n_tiles - 1) & 1, &abort_word));
@@ -361,3 +443,9 @@ cudaError_t attn_dense_tc5_pair(const CUtensorMap_st *mq, const CUtensorMap_st *
 }
 
 }  // namespace h3b
+
+#ifdef H3B_TRACE
+extern "C" cudaError_t h3b_debug_pair_trace(long long *host32) {
+    return cudaMemcpyFromSymbol(host32, h3b::g_pair_trace, sizeof(long long) * 32);
+}
+#endif

@@ -75,6 +75,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Warp-collective bounded wait: lane 0 polls, the warp gets the verdict. 32x fewer probes of
+// the mbarrier word than every lane polling for itself - the probes go to shared memory,
+// which the tensor core is reading its operands from at the same time.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_word) {
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_word);
+    return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+}
+
 // ---- TMA (non-multicast tile loads only) ---------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -191,6 +200,32 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The same two instructions with the 64-bit shared-memory descriptors passed as (low, high)
+// words. Consecutive K-steps of one tile differ only in the address field of the low word, so
+// the issuing thread builds a descriptor once per tile and spends one 32-bit add per MMA - it
+// shares its scheduler with busy softmax warps and every instruction it saves shortens the
+// time the tensor pipe waits for work.
+__device__ __forceinline__ void mma_ss_words(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                             uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_ts_words(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                             uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // The mbarrier receives one arrival once every MMA issued so far by this thread has completed.
