@@ -15,7 +15,9 @@
 //   (cuda/flash3_attention.cu:18-94 in the reference).
 // SPARSE (BN = 64): head-major tiled [H][tiles*64][128] tensors; a CTA pairs two adjacent
 //   64-row query tiles and walks the sorted union of their selected KV tiles, masking each
-//   half against its own list and every KV tile against its valid length. Replaces
+//   half against its own list and every KV tile against its valid length. (Two gathered KV
+//   tiles per step, N = 128, was tried because an N = 64 MMA reaches only two thirds of the
+//   tensor rate; it lost more by giving up the double-buffered S than it gained.) Replaces
 //   fwd_attend_ker<128> (cuda/vendor/vsa_hopper_forward.cuh:68-270) behind h3_vsa_hopper.
 #include <cuda.h>
 
@@ -317,9 +319,9 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             }
             const float neg = (m_ref == -INFINITY) ? 0.0f : -m_ref * p.scale_log2;
             if (nvalid >= BN) {
-                l += exp_store_full<BN>(s_addr, p.scale_log2, neg);
+                l += exp_store_full<BN>(s_addr, s_addr, p.scale_log2, neg);
             } else if (nvalid > 0) {
-                l += exp_store_masked<BN>(s_addr, p.scale_log2, neg, nvalid);
+                l += exp_store_masked<BN>(s_addr, s_addr, p.scale_log2, neg, nvalid);
             } else {
                 store_zero_p<BN>(s_addr);  // this half of the pair did not select the tile
             }

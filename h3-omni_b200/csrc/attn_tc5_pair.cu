@@ -345,7 +345,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                         tmem_wait_st();
                     }
                 }
-                l += exp_store_masked<PBN>(s_addr, p.scale_log2, -m_ref * p.scale_log2, nvalid);
+                l += exp_store_masked<PBN>(s_addr, s_addr, p.scale_log2, -m_ref * p.scale_log2, nvalid);
             }
             if (!saw_prev_pv) {
                 alive = __all_sync(0xffffffffu, mbar_wait(bar_pv_done(t), (j - 1) & 1, &abort_word));

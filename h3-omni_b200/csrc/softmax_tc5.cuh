@@ -72,9 +72,11 @@ __device__ __forceinline__ void exp_chunk(const uint32_t (&v)[32], uint32_t (&pa
         packed[i / 2 + 1] = pack_bf16(p1.x, p1.y);
     }
 }
-// Full tile: P overwrites S in place (bf16 pairs, half the columns), loads one chunk ahead.
+// Full tile: P (bf16 pairs, half the columns) goes to p_addr - over columns of S that were
+// already consumed - with the loads running one chunk ahead.
 template <int BN>
-__device__ __forceinline__ float exp_store_full(uint32_t s_addr, float scale_log2, float neg) {
+__device__ __forceinline__ float exp_store_full(uint32_t s_addr, uint32_t p_addr, float scale_log2,
+                                                float neg) {
     constexpr int NC = BN / 32;
     uint32_t a[32], b[32], packed[16];
     float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
@@ -85,20 +87,20 @@ __device__ __forceinline__ float exp_store_full(uint32_t s_addr, float scale_log
     for (int c = 0; c < NC; c += 2) {
         if (c + 1 < NC) tmem_ld32(s_addr + (c + 1) * 32, b);
         exp_chunk(a, packed, scale2, neg2, sum0, sum1);
-        tmem_st16(s_addr + c * 16, packed);
+        tmem_st16(p_addr + c * 16, packed);
         if (c + 1 < NC) {
             tmem_wait_ld();
             if (c + 2 < NC) tmem_ld32(s_addr + (c + 2) * 32, a);
             exp_chunk(b, packed, scale2, neg2, sum0, sum1);
-            tmem_st16(s_addr + (c + 1) * 16, packed);
+            tmem_st16(p_addr + (c + 1) * 16, packed);
             if (c + 2 < NC) tmem_wait_ld();
         }
     }
     return (sum0.x + sum0.y) + (sum1.x + sum1.y);
 }
 template <int BN>
-__device__ __forceinline__ float exp_store_masked(uint32_t s_addr, float scale_log2, float neg,
-                                                  int nvalid) {
+__device__ __forceinline__ float exp_store_masked(uint32_t s_addr, uint32_t p_addr, float scale_log2,
+                                                  float neg, int nvalid) {
     float sum = 0.0f;
 #pragma unroll
     for (int c = 0; c < BN / 32; c++) {
@@ -114,17 +116,17 @@ __device__ __forceinline__ float exp_store_masked(uint32_t s_addr, float scale_l
             sum += p0 + p1;
             packed[i / 2] = pack_bf16(p0, p1);
         }
-        tmem_st16(s_addr + c * 16, packed);
+        tmem_st16(p_addr + c * 16, packed);
     }
     return sum;
 }
 template <int BN>
-__device__ __forceinline__ void store_zero_p(uint32_t s_addr) {
+__device__ __forceinline__ void store_zero_p(uint32_t p_addr) {
     uint32_t zero[16];
 #pragma unroll
     for (int i = 0; i < 16; i++) zero[i] = 0u;
 #pragma unroll
-    for (int c = 0; c < BN / 32; c++) tmem_st16(s_addr + c * 16, zero);
+    for (int c = 0; c < BN / 32; c++) tmem_st16(p_addr + c * 16, zero);
 }
 
 
