@@ -205,6 +205,16 @@ def main():
             raise RuntimeError(err.value.decode())
         comm = handle
 
+    if args.workload != "dense":
+        # Secondary workloads on one GPU: the sparse (C3) or the KV-history (C5) path alone.
+        if world != 1:
+            raise SystemExit("--workload %s runs on one GPU" % args.workload)
+        result = secondary(gpu, torch, device, stream, peaks(), only=args.workload, steps=args.steps)
+        print(json.dumps({"metric": args.workload, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                          "data": "synthetic", "dtype": "bf16", **result[args.workload]}), flush=True)
+        gpu.close()
+        return
+
     plan = ulysses.plan(SEQ, HEADS, world)
     rows, local_heads = plan.shard_rows, plan.local_heads
     shard_elems = rows * HEADS * DIM
@@ -335,12 +345,14 @@ def main():
         dist.destroy_process_group()
 
 
-def secondary(gpu, torch, device, stream, pk):
+def secondary(gpu, torch, device, stream, pk, only=None, steps=5):
     """VSA (coarse + fine + merge) and live KV-history attention on the benchmark shapes."""
     out = {}
     lib = gpu.lib
+    default_steps = steps
 
-    def events(fn, steps=5, warmup=2):
+    def events(fn, steps=None, warmup=2):
+        steps = steps or default_steps
         for _ in range(warmup):
             fn()
         torch.cuda.synchronize()
@@ -352,6 +364,17 @@ def secondary(gpu, torch, device, stream, pk):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / steps
 
+    wrap = lambda t: gpu.wrap(t.data_ptr(), t.numel())
+    g = torch.Generator(device=device)
+    if only in (None, "vsa"):
+        vsa_part(gpu, torch, device, pk, out, events, wrap, g)
+    if only in (None, "live"):
+        live_part(gpu, torch, device, out, events, wrap, g)
+    return out
+
+
+def vsa_part(gpu, torch, device, pk, out, events, wrap, g):
+    lib = gpu.lib
     # --- VSA: text 64 + audio 512 prefix, video 32x30x54 -> 896 cubes, keep 12.5 % ---
     text, audio, grid = 64, 512, (32, 30, 54)
     vsa = gpu.call("vsa_new", text, audio, *grid, HEADS)
@@ -360,13 +383,11 @@ def secondary(gpu, torch, device, stream, pk):
     rows, tiles, prefix, _ = (x.value for x in info)
     keep = (tiles - prefix) // 8
     lib.h3b_vsa_set_keep(vsa, keep)
-    g = torch.Generator(device=device)
     g.manual_seed(1003)
     q, k, v = (torch.randn(rows, HEADS, DIM, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
                for _ in range(3))
     gate = (0.3 * torch.randn(rows, HEADS, DIM, generator=g, device=device)).to(torch.bfloat16)
     o = torch.empty_like(q)
-    wrap = lambda t: gpu.wrap(t.data_ptr(), t.numel())
     tq, tk, tv, tg, to = wrap(q), wrap(k), wrap(v), wrap(gate), wrap(o)
 
     def vsa_step():
@@ -396,8 +417,9 @@ def secondary(gpu, torch, device, stream, pk):
         "coarse_frac_of_hbm": coarse_bytes / (total_ms - fine_ms) / 1e6 / pk["hbm_gbs"],
     }
     lib.h3_gpu_vsa_free(vsa)
-    del q, k, v, gate, o
 
+
+def live_part(gpu, torch, device, out, events, wrap, g):
     # --- live: 12,960-row query chunk against 12,960 + history keys, history up to 51,840 ---
     nq = 12960
     g.manual_seed(1005)
@@ -414,7 +436,6 @@ def secondary(gpu, torch, device, stream, pk):
         steps.append({"step": s, "key_rows": nk, "ms": ms, "tflops": 4.0 * nq * nk * HEADS * DIM / ms / 1e9})
     out["live"] = {"workload": "query chunk 12960 rows, keys 12960 + min(step,4)*12960 history rows, H=%d" % HEADS,
                    "steps": steps, "total_ms": sum(x["ms"] for x in steps)}
-    return out
 
 
 if __name__ == "__main__":

@@ -73,7 +73,6 @@ tile_pool_kernel(PoolArgs a, const int *__restrict__ map, const int *__restrict_
 }
 
 // ---- scores + top-k selection + compression -----------------------------------------
-constexpr int QT = 8;        // query tiles per CTA, one warp each for selection/softmax
 constexpr int CHUNK = 32;    // pooled K/V rows staged per step
 constexpr int PADDED = VD + 1;
 
@@ -83,21 +82,26 @@ __device__ __forceinline__ uint32_t sort_key(float f) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-// scores row = scale * fmaf-chain over d = 0..127 (ascending), one fixed order.
-// Selection (cuda/vsa.cuh:47-76): prefix query tiles keep all tiles; video query tiles keep
-// all prefix tiles plus the `keep` best video tiles (ties: lower index first), ascending.
-// Compression (cuda/vsa.cuh:80-166,291-294): softmax over the whole row in the ATen lane
-// order, then sum_k p[k] * poolv[k][:] as one fmaf chain over k ascending.
+// One CTA = 8 * QPW query tiles of one head, 8 warps; warp w owns query tiles w, w + 8, ...
+// for selection, softmax and compression. Pooled K (then V) rows stream through shared
+// memory in chunks of 32, the next chunk's global loads in flight while the current one is
+// used, so each pooled row is read from L2 once per 8 * QPW query tiles.
+//   scores row = scale * fmaf-chain over d = 0..127 (ascending), one fixed order.
+//   Selection (cuda/vsa.cuh:47-76): prefix query tiles keep all tiles; video query tiles keep
+//   all prefix tiles plus the `keep` best video tiles (ties: lower index first), ascending.
+//   Compression (cuda/vsa.cuh:80-166,291-294): softmax over the whole row in the ATen lane
+//   order, then sum_k p[k] * poolv[k][:] as one fmaf chain over k ascending.
+template <int QPW>
 __global__ void __launch_bounds__(256)
 score_select_kernel(const float *__restrict__ poolq, const float *__restrict__ poolk,
                     const float *__restrict__ poolv, float *__restrict__ scores_out,
                     int *__restrict__ indices, int *__restrict__ counts,
                     float *__restrict__ compression, int tiles, int prefix, int keep, float scale) {
+    constexpr int QT = 8 * QPW;
     extern __shared__ float sm[];
     float *row_scores = sm;                               // [QT][tiles]
     float *stage = row_scores + (size_t)QT * tiles;       // [CHUNK][PADDED]
     float *qrows = stage + CHUNK * PADDED;                // [QT][VD]
-    int *hist = reinterpret_cast<int *>(qrows + QT * VD); // [QT][256]
 
     const int head = blockIdx.y, qt0 = blockIdx.x * QT;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -108,29 +112,53 @@ score_select_kernel(const float *__restrict__ poolq, const float *__restrict__ p
         const int qi = i / VD;
         qrows[i] = qi < nq ? poolq[((size_t)head * tiles + qt0 + qi) * VD + (i % VD)] : 0.0f;
     }
-    // Scores: stage CHUNK key rows, then thread (kt_local, query group) does its dot products.
-    for (int k0 = 0; k0 < tiles; k0 += CHUNK) {
-        __syncthreads();
-        for (int i = tid; i < CHUNK * VD; i += 256) {
-            const int r = i / VD, d = i % VD;
-            stage[r * PADDED + d] = k0 + r < tiles ? pk[(size_t)(k0 + r) * VD + d] : 0.0f;
-        }
-        __syncthreads();
-        const int r = tid & 31, qi = tid >> 5;  // 32 key rows x 8 query tiles
-        if (k0 + r < tiles && qi < nq) {
-            float dot = 0.0f;
-            const float *kr = stage + r * PADDED, *qr = qrows + qi * VD;
-#pragma unroll 16
-            for (int d = 0; d < VD; d++) dot = fmaf(qr[d], kr[d], dot);
-            row_scores[(size_t)qi * tiles + k0 + r] = scale * dot;
+    // ---- scores: thread (key row r of the chunk, query group) runs QPW dot products ----
+    {
+        float next[16];   // this thread's 16 elements of the chunk being fetched
+        auto fetch = [&](int k0) {
+#pragma unroll
+            for (int u = 0; u < 16; u++) {
+                const int i = tid + u * 256, r = i / VD, d = i % VD;
+                next[u] = k0 + r < tiles ? __ldg(pk + (size_t)(k0 + r) * VD + d) : 0.0f;
+            }
+        };
+        fetch(0);
+        for (int k0 = 0; k0 < tiles; k0 += CHUNK) {
+            __syncthreads();   // previous chunk fully consumed
+#pragma unroll
+            for (int u = 0; u < 16; u++) {
+                const int i = tid + u * 256;
+                stage[(i / VD) * PADDED + (i % VD)] = next[u];
+            }
+            __syncthreads();
+            if (k0 + CHUNK < tiles) fetch(k0 + CHUNK);
+            const int r = lane;
+            if (k0 + r < tiles) {
+                const float *kr = stage + r * PADDED;
+                float dot[QPW];
+#pragma unroll
+                for (int g = 0; g < QPW; g++) dot[g] = 0.0f;
+#pragma unroll 8
+                for (int d = 0; d < VD; d++) {
+                    const float kv = kr[d];
+#pragma unroll
+                    for (int g = 0; g < QPW; g++) dot[g] = fmaf(qrows[(warp + 8 * g) * VD + d], kv, dot[g]);
+                }
+#pragma unroll
+                for (int g = 0; g < QPW; g++)
+                    if (warp + 8 * g < nq) row_scores[(size_t)(warp + 8 * g) * tiles + k0 + r] = scale * dot[g];
+            }
         }
     }
     __syncthreads();
 
-    // ---- selection: warp `warp` owns query tile qt0 + warp ----
-    const int qt = qt0 + warp;
-    float *mine = row_scores + (size_t)warp * tiles;
-    if (warp < nq) {
+    // ---- selection and pooled softmax: warp `warp` owns query tiles qt0 + warp + 8 g ----
+#pragma unroll 1
+    for (int g = 0; g < QPW; g++) {
+        const int qi = warp + 8 * g;
+        if (qi >= nq) break;
+        const int qt = qt0 + qi;
+        float *mine = row_scores + (size_t)qi * tiles;
         const size_t row = (size_t)head * tiles + qt;
         if (scores_out)
             for (int j = lane; j < tiles; j += 32) scores_out[row * tiles + j] = mine[j];
@@ -139,56 +167,26 @@ score_select_kernel(const float *__restrict__ poolq, const float *__restrict__ p
             for (int j = lane; j < tiles; j += 32) dst[j] = j;
             if (lane == 0) counts[row] = tiles;
         } else {
-            // Radix select of the keep-th largest key among video tiles, 8 bits per pass.
-            int *h = hist + warp * 256;
-            uint32_t want = 0u, mask = 0u;
-            int remaining = keep;
-            for (int pass = 3; pass >= 0; pass--) {
-                for (int b = lane; b < 256; b += 32) h[b] = 0;
-                __syncwarp();
-                for (int j = prefix + lane; j < tiles; j += 32) {
-                    const uint32_t key = sort_key(mine[j]);
-                    if ((key & mask) == want) atomicAdd(&h[(key >> (8 * pass)) & 255u], 1);
-                }
-                __syncwarp();
-                // lane L owns bins 255-8L .. 248-8L, highest first
-                int local[8], sum = 0;
+            // The keep-th largest key among the video tiles, found bit by bit from the top:
+            // `want` grows by a bit whenever at least `keep` keys are still >= the candidate.
+            // Counting is a compare per key and one warp reduction per bit - no shared-memory
+            // histogram, no atomics.
+            uint32_t want = 0u;
+            for (int bit = 31; bit >= 0; bit--) {
+                const uint32_t candidate = want | (1u << bit);
+                int count = 0;
+                for (int j = prefix + lane; j < tiles; j += 32) count += sort_key(mine[j]) >= candidate;
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    local[i] = h[255 - 8 * lane - i];
-                    sum += local[i];
-                }
-                int before = sum;  // inclusive scan over lanes, then make it exclusive
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int up = __shfl_up_sync(0xffffffffu, before, o);
-                    if (lane >= o) before += up;
-                }
-                before -= sum;
-                const bool owner = before < remaining && remaining <= before + sum;
-                int bin = 0, above = 0;
-                if (owner) {
-                    int acc = before;
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        if (acc < remaining && remaining <= acc + local[i]) {
-                            bin = 255 - 8 * lane - i;
-                            above = acc;
-                        }
-                        acc += local[i];
-                    }
-                }
-                const unsigned who = __ballot_sync(0xffffffffu, owner);
-                const int src = who ? __ffs(who) - 1 : 0;
-                bin = __shfl_sync(0xffffffffu, bin, src);
-                above = __shfl_sync(0xffffffffu, above, src);
-                remaining -= above;
-                want |= (uint32_t)bin << (8 * pass);
-                mask |= 0xffu << (8 * pass);
-                __syncwarp();
+                for (int o = 16; o; o >>= 1) count += __shfl_xor_sync(0xffffffffu, count, o);
+                if (count >= keep) want = candidate;
             }
-            // `want` is the threshold key; take every larger key and the first `remaining`
-            // equal keys in index order; emit ascending.
+            int greater = 0;
+            for (int j = prefix + lane; j < tiles; j += 32) greater += sort_key(mine[j]) > want;
+#pragma unroll
+            for (int o = 16; o; o >>= 1) greater += __shfl_xor_sync(0xffffffffu, greater, o);
+            const int remaining = keep - greater;   // how many keys equal to `want` to take
+            // Take every larger key and the first `remaining` equal keys in index order;
+            // emit ascending.
             int written = 0, equal_seen = 0;
             for (int base = 0; base < tiles; base += 32) {
                 const int j = base + lane;
@@ -212,16 +210,15 @@ score_select_kernel(const float *__restrict__ poolq, const float *__restrict__ p
             }
             if (lane == 0) counts[row] = written;
         }
-    }
+        if (!compression) continue;
 
-    // ---- pooled softmax (in place, ATen reduction order) ----
-    if (compression && warp < nq) {
+        // pooled softmax, in place, ATen reduction order
         float largest = -CUDART_INF_F, total = 0.0f;
-        if (tiles <= 2048) {
-            for (int j = lane; j < tiles; j += 32) largest = fmaxf(largest, mine[j]);
+        for (int j = lane; j < tiles; j += 32) largest = fmaxf(largest, mine[j]);
 #pragma unroll
-            for (int o = 16; o; o >>= 1)
-                largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, o));
+        for (int o = 16; o; o >>= 1)
+            largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, o));
+        if (tiles <= 2048) {
             for (int j = lane; j < tiles; j += 32) {
                 const float e = expf(mine[j] - largest);
                 mine[j] = e;
@@ -232,10 +229,6 @@ score_select_kernel(const float *__restrict__ poolq, const float *__restrict__ p
         } else {
             // 1024-thread two-level shuffle-down order of the reference's block variant:
             // virtual thread t = w*32 + lane sums columns t, t+1024, ...
-            for (int j = lane; j < tiles; j += 32) largest = fmaxf(largest, mine[j]);
-#pragma unroll
-            for (int o = 16; o; o >>= 1)
-                largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, o));
             float warp_sums = 0.0f;  // lane w keeps virtual warp w's sum
             for (int w = 0; w < 32; w++) {
                 float part = 0.0f;
@@ -244,18 +237,12 @@ score_select_kernel(const float *__restrict__ poolq, const float *__restrict__ p
                     if (col < tiles) part += expf(mine[col] - largest);
                 }
 #pragma unroll
-                for (int o = 16; o; o >>= 1) {
-                    const float other = __shfl_down_sync(0xffffffffu, part, o);
-                    part += other;
-                }
+                for (int o = 16; o; o >>= 1) part += __shfl_down_sync(0xffffffffu, part, o);
                 part = __shfl_sync(0xffffffffu, part, 0);
                 if (lane == w) warp_sums = part;
             }
 #pragma unroll
-            for (int o = 16; o; o >>= 1) {
-                const float other = __shfl_down_sync(0xffffffffu, warp_sums, o);
-                warp_sums += other;
-            }
+            for (int o = 16; o; o >>= 1) warp_sums += __shfl_down_sync(0xffffffffu, warp_sums, o);
             total = __shfl_sync(0xffffffffu, warp_sums, 0);
             for (int j = lane; j < tiles; j += 32) mine[j] = expf(mine[j] - largest);
         }
@@ -264,33 +251,46 @@ score_select_kernel(const float *__restrict__ poolq, const float *__restrict__ p
     }
     if (!compression) return;
 
-    // ---- compression: lane owns dims 4*lane..4*lane+3 of its warp's query tile ----
+    // ---- compression: lane owns dims 4*lane..4*lane+3 of each of its warp's query tiles ----
     const float *pv = poolv + (size_t)head * tiles * VD;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 acc[QPW];
+#pragma unroll
+    for (int g = 0; g < QPW; g++) acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 *stage4 = reinterpret_cast<float4 *>(stage);  // [CHUNK][VD/4], unpadded reuse
+    float4 next4[4];
+    auto fetch4 = [&](int k0) {
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = tid + u * 256, r = i / (VD / 4);
+            next4[u] = k0 + r < tiles
+                           ? __ldg(reinterpret_cast<const float4 *>(pv + (size_t)(k0 + r) * VD) + i % (VD / 4))
+                           : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    fetch4(0);
     for (int k0 = 0; k0 < tiles; k0 += CHUNK) {
         __syncthreads();
-        for (int i = tid; i < CHUNK * (VD / 4); i += 256) {
-            const int r = i / (VD / 4);
-            stage4[i] = k0 + r < tiles
-                            ? reinterpret_cast<const float4 *>(pv + (size_t)(k0 + r) * VD)[i % (VD / 4)]
-                            : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) stage4[tid + u * 256] = next4[u];
         __syncthreads();
-        if (warp < nq) {
-            const int n = min(CHUNK, tiles - k0);
-            for (int r = 0; r < n; r++) {
-                const float pr = mine[k0 + r];
-                const float4 vv = stage4[r * (VD / 4) + lane];
-                acc.x = fmaf(pr, vv.x, acc.x);
-                acc.y = fmaf(pr, vv.y, acc.y);
-                acc.z = fmaf(pr, vv.z, acc.z);
-                acc.w = fmaf(pr, vv.w, acc.w);
+        if (k0 + CHUNK < tiles) fetch4(k0 + CHUNK);
+        const int n = min(CHUNK, tiles - k0);
+        for (int r = 0; r < n; r++) {
+            const float4 vv = stage4[r * (VD / 4) + lane];
+#pragma unroll
+            for (int g = 0; g < QPW; g++) {
+                const float pr = row_scores[(size_t)(warp + 8 * g) * tiles + k0 + r];
+                acc[g].x = fmaf(pr, vv.x, acc[g].x);
+                acc[g].y = fmaf(pr, vv.y, acc[g].y);
+                acc[g].z = fmaf(pr, vv.z, acc[g].z);
+                acc[g].w = fmaf(pr, vv.w, acc[g].w);
             }
         }
     }
-    if (warp < nq)
-        reinterpret_cast<float4 *>(compression + ((size_t)head * tiles + qt) * VD)[lane] = acc;
+#pragma unroll
+    for (int g = 0; g < QPW; g++)
+        if (warp + 8 * g < nq)
+            reinterpret_cast<float4 *>(compression + ((size_t)head * tiles + qt0 + warp + 8 * g) * VD)[lane] = acc[g];
 }
 
 // ---- merge ---------------------------------------------------------------------------
@@ -344,8 +344,30 @@ cudaError_t vsa_tile_pool3(const void *const src[3], void *const tiled[3], float
     return cudaGetLastError();
 }
 
-static size_t score_select_smem(int tiles) {
-    return sizeof(float) * ((size_t)QT * tiles + CHUNK * PADDED + QT * VD) + sizeof(int) * QT * 256;
+static size_t score_select_smem(int tiles, int qt) {
+    return sizeof(float) * ((size_t)qt * tiles + CHUNK * PADDED + (size_t)qt * VD);
+}
+
+template <int QPW>
+static cudaError_t launch_score_select(const float *poolq, const float *poolk, const float *poolv,
+                                       float *scores, int *indices, int *counts, float *compression,
+                                       int tiles, int prefix, int keep, int heads, float scale,
+                                       cudaStream_t stream) {
+    constexpr int QT = 8 * QPW;
+    static thread_local int configured_device = -1;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (configured_device != device) {
+        e = cudaFuncSetAttribute(score_select_kernel<QPW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)score_select_smem(QPW == 1 ? 4096 : 2048, QT));
+        if (e != cudaSuccess) return e;
+        configured_device = device;
+    }
+    dim3 grid((tiles + QT - 1) / QT, heads);
+    score_select_kernel<QPW><<<grid, 256, score_select_smem(tiles, QT), stream>>>(
+        poolq, poolk, poolv, scores, indices, counts, compression, tiles, prefix, keep, scale);
+    return cudaGetLastError();
 }
 
 cudaError_t vsa_score_select_compress(const float *poolq, const float *poolk, const float *poolv,
@@ -354,23 +376,12 @@ cudaError_t vsa_score_select_compress(const float *poolq, const float *poolk, co
                                       int heads, float scale, cudaStream_t stream) {
     if (tiles < 1 || tiles > 4096 || keep < 1 || prefix < 0 || prefix > tiles)
         return cudaErrorInvalidValue;
-    const size_t smem = score_select_smem(tiles);
-    static thread_local size_t configured = 0;
-    static thread_local int configured_device = -1;
-    int device = 0;
-    cudaError_t e = cudaGetDevice(&device);
-    if (e != cudaSuccess) return e;
-    if (configured_device != device || smem > configured) {
-        e = cudaFuncSetAttribute(score_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)score_select_smem(4096));
-        if (e != cudaSuccess) return e;
-        configured = score_select_smem(4096);
-        configured_device = device;
-    }
-    dim3 grid((tiles + QT - 1) / QT, heads);
-    score_select_kernel<<<grid, 256, smem, stream>>>(poolq, poolk, poolv, scores, indices, counts,
-                                                     compression, tiles, prefix, keep, scale);
-    return cudaGetLastError();
+    // 16 query tiles per CTA while two CTAs still fit an SM, 8 beyond that.
+    if (tiles <= 1400)
+        return launch_score_select<2>(poolq, poolk, poolv, scores, indices, counts, compression, tiles,
+                                      prefix, keep, heads, scale, stream);
+    return launch_score_select<1>(poolq, poolk, poolv, scores, indices, counts, compression, tiles,
+                                  prefix, keep, heads, scale, stream);
 }
 
 cudaError_t vsa_untile_merge(void *output, const void *tiled, const void *gate,
