@@ -23,13 +23,14 @@ __device__ __forceinline__ uint32_t f32_to_bf16_bits(float x) {
 __device__ __forceinline__ float bf16_round(float x) { return bf16_bits_to_f32(f32_to_bf16_bits(x)); }
 
 // ---- pooling ---------------------------------------------------------------------
-// One CTA = one tile x 4 heads x one of {Q, K, V}; thread = (head, pair of dims), so every
-// token row contributes one contiguous 1 KB read per CTA. The per-dimension summation order
-// is the reference's (cuda/vsa.cuh:22-42): 4 lanes x 4 slot accumulators, element
-// i = lane + 4*slot + 16*round, ((a0+a1)+a2)+a3 per lane, (l0+l2)+(l1+l3), then / size.
+// One CTA = one tile x 8 heads x one of {Q, K, V}; thread = (head, four dims = 8 bytes), so
+// every token row contributes one contiguous 2 KB read per CTA and each thread keeps 64
+// independent 8-byte loads in flight. The per-dimension summation order is the reference's
+// (cuda/vsa.cuh:22-42): 4 lanes x 4 slot accumulators, element i = lane + 4*slot + 16*round,
+// ((a0+a1)+a2)+a3 per lane, (l0+l2)+(l1+l3), then / size.
 struct PoolArgs {
-    const uint32_t *src[3];
-    uint32_t *tiled[3];
+    const uint2 *src[3];
+    uint2 *tiled[3];
     float *pooled[3];
 };
 
@@ -38,43 +39,52 @@ tile_pool_kernel(PoolArgs a, const int *__restrict__ map, const int *__restrict_
                  int heads) {
     __shared__ int rows[VT];
     const int tile = blockIdx.x, which = blockIdx.z;
-    const int head = blockIdx.y * 4 + (threadIdx.x >> 6), dp = threadIdx.x & 63;
+    const int head = blockIdx.y * 8 + (threadIdx.x >> 5), dq = threadIdx.x & 31;
     if (threadIdx.x < VT) rows[threadIdx.x] = map[tile * VT + threadIdx.x];
     __syncthreads();
     if (head >= heads) return;
-    const uint32_t *src = a.src[which];
-    uint32_t *tiled = a.tiled[which];
-    float lane_lo[4], lane_hi[4];
+    const uint2 *src = which == 0 ? a.src[0] : which == 1 ? a.src[1] : a.src[2];
+    uint2 *tiled = which == 0 ? a.tiled[0] : which == 1 ? a.tiled[1] : a.tiled[2];
+    float *pooled = which == 0 ? a.pooled[0] : which == 1 ? a.pooled[1] : a.pooled[2];
+    float lane_sum[4][4];   // [lane][dim]
 #pragma unroll
     for (int lane = 0; lane < 4; lane++) {
-        float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
+        float acc[4][4];    // [slot][dim]
+#pragma unroll
+        for (int slot = 0; slot < 4; slot++)
+#pragma unroll
+            for (int d = 0; d < 4; d++) acc[slot][d] = 0.0f;
 #pragma unroll
         for (int round = 0; round < 4; round++) {
 #pragma unroll
             for (int slot = 0; slot < 4; slot++) {
                 const int i = lane + slot * 4 + round * 16;
                 const int row = rows[i];
-                const uint32_t x =
-                    row < 0 ? 0u : __ldg(src + ((size_t)row * heads + head) * (VD / 2) + dp);
-                if (tiled)
-                    tiled[((size_t)head * tiles * VT + tile * VT + i) * (VD / 2) + dp] = x;
-                lo[slot] += bf16_bits_to_f32(x & 0xffffu);
-                hi[slot] += bf16_bits_to_f32(x >> 16);
+                uint2 x = make_uint2(0u, 0u);
+                if (row >= 0) x = __ldg(src + ((size_t)row * heads + head) * (VD / 4) + dq);
+                if (tiled) tiled[((size_t)head * tiles * VT + tile * VT + i) * (VD / 4) + dq] = x;
+                acc[slot][0] += bf16_bits_to_f32(x.x & 0xffffu);
+                acc[slot][1] += bf16_bits_to_f32(x.x >> 16);
+                acc[slot][2] += bf16_bits_to_f32(x.y & 0xffffu);
+                acc[slot][3] += bf16_bits_to_f32(x.y >> 16);
             }
         }
-        lane_lo[lane] = ((lo[0] + lo[1]) + lo[2]) + lo[3];
-        lane_hi[lane] = ((hi[0] + hi[1]) + hi[2]) + hi[3];
+#pragma unroll
+        for (int d = 0; d < 4; d++)
+            lane_sum[lane][d] = ((acc[0][d] + acc[1][d]) + acc[2][d]) + acc[3][d];
     }
     const float size = (float)sizes[tile];
-    float2 mean;
-    mean.x = ((lane_lo[0] + lane_lo[2]) + (lane_lo[1] + lane_lo[3])) / size;
-    mean.y = ((lane_hi[0] + lane_hi[2]) + (lane_hi[1] + lane_hi[3])) / size;
-    reinterpret_cast<float2 *>(a.pooled[which])[((size_t)head * tiles + tile) * (VD / 2) + dp] = mean;
+    float4 mean;
+    mean.x = ((lane_sum[0][0] + lane_sum[2][0]) + (lane_sum[1][0] + lane_sum[3][0])) / size;
+    mean.y = ((lane_sum[0][1] + lane_sum[2][1]) + (lane_sum[1][1] + lane_sum[3][1])) / size;
+    mean.z = ((lane_sum[0][2] + lane_sum[2][2]) + (lane_sum[1][2] + lane_sum[3][2])) / size;
+    mean.w = ((lane_sum[0][3] + lane_sum[2][3]) + (lane_sum[1][3] + lane_sum[3][3])) / size;
+    reinterpret_cast<float4 *>(pooled)[((size_t)head * tiles + tile) * (VD / 4) + dq] = mean;
 }
 
 // ---- scores + top-k selection + compression -----------------------------------------
-constexpr int CHUNK = 32;    // pooled K/V rows staged per step
-constexpr int PADDED = VD + 1;
+constexpr int CHUNK = 64;    // pooled K/V rows staged per step
+constexpr int PADDED = VD + 4;  // 16-byte aligned rows; float4 reads of 8 consecutive rows hit 32 distinct banks
 
 // Order-preserving key of a float, the one cub's radix sort uses: larger float -> larger key.
 __device__ __forceinline__ uint32_t sort_key(float f) {
@@ -112,41 +122,51 @@ score_select_kernel(const float *__restrict__ poolq, const float *__restrict__ p
         const int qi = i / VD;
         qrows[i] = qi < nq ? poolq[((size_t)head * tiles + qt0 + qi) * VD + (i % VD)] : 0.0f;
     }
-    // ---- scores: thread (key row r of the chunk, query group) runs QPW dot products ----
+    // ---- scores: thread = (key row r of the chunk, query group); 4 * QPW dot products per
+    // thread from float4 shared-memory reads (the pass is bound by shared-memory wavefronts:
+    // 4 for the key vector + 1 per broadcast query vector feed 16 * QPW FMAs) ----
     {
-        float next[16];   // this thread's 16 elements of the chunk being fetched
+        constexpr int NQ = 4 * QPW;            // query rows per thread: group + 4 g... (QT / 4)
+        constexpr int PER_THREAD = CHUNK * VD / 256;
+        float next[PER_THREAD];   // this thread's elements of the chunk being fetched
         auto fetch = [&](int k0) {
 #pragma unroll
-            for (int u = 0; u < 16; u++) {
+            for (int u = 0; u < PER_THREAD; u++) {
                 const int i = tid + u * 256, r = i / VD, d = i % VD;
                 next[u] = k0 + r < tiles ? __ldg(pk + (size_t)(k0 + r) * VD + d) : 0.0f;
             }
         };
         fetch(0);
+        const int r = tid & (CHUNK - 1), group = tid / CHUNK;   // 64 key rows x 4 query groups
         for (int k0 = 0; k0 < tiles; k0 += CHUNK) {
             __syncthreads();   // previous chunk fully consumed
 #pragma unroll
-            for (int u = 0; u < 16; u++) {
+            for (int u = 0; u < PER_THREAD; u++) {
                 const int i = tid + u * 256;
                 stage[(i / VD) * PADDED + (i % VD)] = next[u];
             }
             __syncthreads();
             if (k0 + CHUNK < tiles) fetch(k0 + CHUNK);
-            const int r = lane;
             if (k0 + r < tiles) {
-                const float *kr = stage + r * PADDED;
-                float dot[QPW];
+                const float4 *kr = reinterpret_cast<const float4 *>(stage + r * PADDED);
+                float dot[NQ];
 #pragma unroll
-                for (int g = 0; g < QPW; g++) dot[g] = 0.0f;
-#pragma unroll 8
-                for (int d = 0; d < VD; d++) {
-                    const float kv = kr[d];
+                for (int g = 0; g < NQ; g++) dot[g] = 0.0f;
+#pragma unroll 4
+                for (int d4 = 0; d4 < VD / 4; d4++) {
+                    const float4 kv = kr[d4];
 #pragma unroll
-                    for (int g = 0; g < QPW; g++) dot[g] = fmaf(qrows[(warp + 8 * g) * VD + d], kv, dot[g]);
+                    for (int g = 0; g < NQ; g++) {
+                        const float4 qv = reinterpret_cast<const float4 *>(qrows + (group + 4 * g) * VD)[d4];
+                        dot[g] = fmaf(qv.x, kv.x, dot[g]);
+                        dot[g] = fmaf(qv.y, kv.y, dot[g]);
+                        dot[g] = fmaf(qv.z, kv.z, dot[g]);
+                        dot[g] = fmaf(qv.w, kv.w, dot[g]);
+                    }
                 }
 #pragma unroll
-                for (int g = 0; g < QPW; g++)
-                    if (warp + 8 * g < nq) row_scores[(size_t)(warp + 8 * g) * tiles + k0 + r] = scale * dot[g];
+                for (int g = 0; g < NQ; g++)
+                    if (group + 4 * g < nq) row_scores[(size_t)(group + 4 * g) * tiles + k0 + r] = scale * dot[g];
             }
         }
     }
@@ -172,18 +192,35 @@ score_select_kernel(const float *__restrict__ poolq, const float *__restrict__ p
             // Counting is a compare per key and one warp reduction per bit - no shared-memory
             // histogram, no atomics.
             uint32_t want = 0u;
-            for (int bit = 31; bit >= 0; bit--) {
-                const uint32_t candidate = want | (1u << bit);
-                int count = 0;
-                for (int j = prefix + lane; j < tiles; j += 32) count += sort_key(mine[j]) >= candidate;
-#pragma unroll
-                for (int o = 16; o; o >>= 1) count += __shfl_xor_sync(0xffffffffu, count, o);
-                if (count >= keep) want = candidate;
-            }
             int greater = 0;
-            for (int j = prefix + lane; j < tiles; j += 32) greater += sort_key(mine[j]) > want;
+            if (tiles - prefix <= 32 * 32) {
+                // up to 1024 video tiles: this lane's keys live in registers for all 33 passes
+                uint32_t key[32];
 #pragma unroll
-            for (int o = 16; o; o >>= 1) greater += __shfl_xor_sync(0xffffffffu, greater, o);
+                for (int i = 0; i < 32; i++) {
+                    const int j = prefix + lane + 32 * i;
+                    key[i] = j < tiles ? sort_key(mine[j]) : 0u;   // 0 is below every real key
+                }
+                for (int bit = 31; bit >= 0; bit--) {
+                    const uint32_t candidate = want | (1u << bit);
+                    int count = 0;
+#pragma unroll
+                    for (int i = 0; i < 32; i++) count += key[i] >= candidate;
+                    if (__reduce_add_sync(0xffffffffu, count) >= keep) want = candidate;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i++) greater += key[i] > want;
+                greater = __reduce_add_sync(0xffffffffu, greater);
+            } else {
+                for (int bit = 31; bit >= 0; bit--) {
+                    const uint32_t candidate = want | (1u << bit);
+                    int count = 0;
+                    for (int j = prefix + lane; j < tiles; j += 32) count += sort_key(mine[j]) >= candidate;
+                    if (__reduce_add_sync(0xffffffffu, count) >= keep) want = candidate;
+                }
+                for (int j = prefix + lane; j < tiles; j += 32) greater += sort_key(mine[j]) > want;
+                greater = __reduce_add_sync(0xffffffffu, greater);
+            }
             const int remaining = keep - greater;   // how many keys equal to `want` to take
             // Take every larger key and the first `remaining` equal keys in index order;
             // emit ascending.
@@ -257,10 +294,11 @@ score_select_kernel(const float *__restrict__ poolq, const float *__restrict__ p
 #pragma unroll
     for (int g = 0; g < QPW; g++) acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 *stage4 = reinterpret_cast<float4 *>(stage);  // [CHUNK][VD/4], unpadded reuse
-    float4 next4[4];
+    constexpr int PER_THREAD4 = CHUNK * (VD / 4) / 256;
+    float4 next4[PER_THREAD4];
     auto fetch4 = [&](int k0) {
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < PER_THREAD4; u++) {
             const int i = tid + u * 256, r = i / (VD / 4);
             next4[u] = k0 + r < tiles
                            ? __ldg(reinterpret_cast<const float4 *>(pv + (size_t)(k0 + r) * VD) + i % (VD / 4))
@@ -271,7 +309,7 @@ score_select_kernel(const float *__restrict__ poolq, const float *__restrict__ p
     for (int k0 = 0; k0 < tiles; k0 += CHUNK) {
         __syncthreads();
 #pragma unroll
-        for (int u = 0; u < 4; u++) stage4[tid + u * 256] = next4[u];
+        for (int u = 0; u < PER_THREAD4; u++) stage4[tid + u * 256] = next4[u];
         __syncthreads();
         if (k0 + CHUNK < tiles) fetch4(k0 + CHUNK);
         const int n = min(CHUNK, tiles - k0);
@@ -335,11 +373,11 @@ cudaError_t vsa_tile_pool3(const void *const src[3], void *const tiled[3], float
                            cudaStream_t stream) {
     PoolArgs a{};
     for (int i = 0; i < count; i++) {
-        a.src[i] = static_cast<const uint32_t *>(src[i]);
-        a.tiled[i] = static_cast<uint32_t *>(tiled[i]);
+        a.src[i] = static_cast<const uint2 *>(src[i]);
+        a.tiled[i] = static_cast<uint2 *>(tiled[i]);
         a.pooled[i] = pooled[i];
     }
-    dim3 grid(tiles, (heads + 3) / 4, count);
+    dim3 grid(tiles, (heads + 7) / 8, count);
     tile_pool_kernel<<<grid, 256, 0, stream>>>(a, map, sizes, tiles, heads);
     return cudaGetLastError();
 }
