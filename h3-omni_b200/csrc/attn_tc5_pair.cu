@@ -105,7 +105,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const uint32_t tmem = tmem_slot;
 
     if (warp >= 8) {
-    warpgroup_reg_dec<56>();
+    warpgroup_reg_dec<88>();
     if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
@@ -180,16 +180,25 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             }
             for (int j = 0; alive && j < n_tiles; j++) {
                 const bool more = j + 1 < n_tiles;
-                {
-                    TRACE_T0();
-                    if (!mbar_wait(bar_p_full(0), j & 1, &abort_word)) break;
-                    TRACE_ADD(0);
-                }
+                // K/V of this step were requested a step ago; probe them first so that these
+                // (normally immediate) waits are off the path between P arriving and the PV issue.
                 {
                     TRACE_T0();
                     if (!wait_stage(2 * j + 1)) break;
                     TRACE_ADD(1);
                 }
+                if (more) {
+                    TRACE_T0();
+                    if (!wait_stage(2 * j + 2)) break;
+                    TRACE_ADD(2);
+                }
+#ifndef H3B_EXP_NO_PWAIT
+                {
+                    TRACE_T0();
+                    if (!mbar_wait(bar_p_full(0), j & 1, &abort_word)) break;
+                    TRACE_ADD(0);
+                }
+#endif
                 tc5_fence_after();
                 {
                     TRACE_T0();
@@ -197,21 +206,17 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     TRACE_ADD(4);
                 }
                 if (more) {
-                    {
-                        TRACE_T0();
-                        if (!wait_stage(2 * j + 2)) break;
-                        TRACE_ADD(2);
-                    }
-                    tc5_fence_after();
                     TRACE_T0();
                     issue_qk(j + 1, 0);
                     TRACE_ADD(5);
                 }
+#ifndef H3B_EXP_NO_PWAIT
                 {
                     TRACE_T0();
                     if (!mbar_wait(bar_p_full(1), j & 1, &abort_word)) break;
                     TRACE_ADD(3);
                 }
+#endif
                 tc5_fence_after();
                 issue_pv(j, 1);
                 mma_commit(bar_empty((2 * j + 1) % ST));
@@ -235,7 +240,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
     }
     } else {
-        warpgroup_reg_inc<224>();
+        warpgroup_reg_inc<208>();
         // ------------------------------ online softmax ------------------------------
         const int t = warp >> 2;                // which query tile
         const int r = tid & 127;                // row inside the tile == TMEM lane
