@@ -328,6 +328,9 @@ def main():
         "clocks": clocks,
     }
 
+    dit = None
+    if not args.no_also and not args.sequence:
+        dit = dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_over_ranks)
     if rank == 0 and world == 1:
         oracle = entry.load_oracle()
         oracle.build()
@@ -336,6 +339,8 @@ def main():
                                 "sample": sample, "seconds": seconds}
         if not args.no_also and not args.sequence:
             line["also"] = secondary(gpu, torch, device, stream, pk)
+    if dit is not None:
+        line.setdefault("also", {})["dit_step"] = dit
     if rank == 0:
         print(json.dumps(line), flush=True)
     if comm is not None:
@@ -343,6 +348,75 @@ def main():
     gpu.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_over_ranks, blocks=50, steps=2):
+    """One denoising step of the 50-block DiT at the benchmark shape, timed at N GPUs.
+
+    Op order of the reference's run_block (h3_dit.c:2450-2673) with the reference's widths
+    (hidden 5376, FFN 14336, h3_dit.c:20-35) and the benchmark's 24 heads. Attention and the
+    Ulysses exchanges are this library's; the projections and MLP are torch bf16 GEMMs and the
+    elementwise ops (AdaLN, per-head RMS norm, SwiGLU, gates) are plain torch ops standing in for
+    the reference's own kernels, which are outside this library. One block's synthetic weights
+    are reused for all blocks. Reported for the scaling picture only."""
+    hidden, ffn, inner = 5376, 14336, HEADS * DIM
+    rows, local_heads = plan.shard_rows, plan.local_heads
+    g = torch.Generator(device=device)
+    g.manual_seed(4242)
+    rand = lambda *shape, fan: (torch.randn(*shape, generator=g, device=device) / fan ** 0.5).to(torch.bfloat16)
+    w_qkv, w_out = rand(hidden, 3 * inner, fan=hidden), rand(inner, hidden, fan=inner)
+    w_fc1, w_fc2 = rand(hidden, 2 * ffn, fan=hidden), rand(ffn, hidden, fan=ffn)
+    mod = (0.1 * torch.randn(6, hidden, generator=g, device=device)).to(torch.bfloat16)
+    x0 = torch.randn(rows, hidden, generator=g, device=device).to(torch.bfloat16)
+    q, k, v = (torch.empty(rows, HEADS, DIM, device=device, dtype=torch.bfloat16) for _ in range(3))
+    o = torch.empty_like(q)
+    scratch = torch.empty_like(q)
+    gathered = torch.empty(world * rows, hidden, device=device, dtype=torch.bfloat16) if world > 1 else None
+    wrap = lambda t: gpu.wrap(t.data_ptr(), t.numel())
+    tq, tk, tv, to, tscr = wrap(q), wrap(k), wrap(v), wrap(o), wrap(scratch)
+    F = torch.nn.functional
+
+    def norm_mod(x, scale, shift):
+        return F.rms_norm(x, (hidden,)) * (1 + scale) + shift
+
+    def forward():
+        x = x0.clone()
+        for _ in range(blocks):
+            h = norm_mod(x, mod[0], mod[1])
+            qkv = (h @ w_qkv).view(rows, 3, HEADS, DIM)
+            q.copy_(F.rms_norm(qkv[:, 0], (DIM,)))       # stands in for QK-RMS + RoPE writing Q, K, V
+            k.copy_(F.rms_norm(qkv[:, 1], (DIM,)))
+            v.copy_(qkv[:, 2])
+            if world > 1:
+                for t in (tq, tk, tv):
+                    gpu.call("ulysses_scatter_heads_bf16", comm, t, tscr, rows, HEADS, DIM)
+            gpu.call("sdpa_bf16", to, tq, tk, tv, plan.sequence, local_heads, DIM, SCALE)
+            if world > 1:
+                gpu.call("ulysses_gather_heads_bf16", comm, to, tscr, rows, HEADS, DIM)
+            x = x + mod[2] * (o.view(rows, inner) @ w_out)
+            h = norm_mod(x, mod[3], mod[4])
+            u = h @ w_fc1
+            x = x + mod[5] * ((F.silu(u[:, :ffn]) * u[:, ffn:]) @ w_fc2)
+        if world > 1:
+            tx, tg = wrap(x), wrap(gathered)
+            gpu.call("all_gather_bf16", comm, tg, tx, rows * hidden)
+        return x
+
+    forward()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(steps):
+        forward()
+    b.record(stream)
+    barrier()
+    ms = max_over_ranks(a.elapsed_time(b) / steps)
+    gemm_flops = 2.0 * plan.sequence * (hidden * 3 * inner + inner * hidden + hidden * 2 * ffn + ffn * hidden) * blocks
+    attn_flops = 4.0 * plan.sequence ** 2 * HEADS * DIM * blocks
+    return {"workload": "50-block DiT denoising step, L=%d, H=%d, hidden %d, FFN %d; attention + Ulysses exchanges from "
+                        "this library, GEMMs and elementwise ops torch" % (plan.sequence, HEADS, hidden, ffn),
+            "ms_per_step": ms, "n_gpus": world, "steps": steps, "blocks": blocks,
+            "model_tflops": (gemm_flops + attn_flops) / ms / 1e9}
 
 
 def secondary(gpu, torch, device, stream, pk, only=None, steps=5):
