@@ -30,6 +30,8 @@ import __graft_entry__ as entry  # noqa: E402
 SEQ_VIDEO, SEQ_AUDIO, HEADS, DIM = 51840, 512, 24, 128
 SEQ = SEQ_VIDEO + SEQ_AUDIO
 SCALE = float(1.0 / np.sqrt(128.0))
+EXCHANGE_NOTE = "fused peer-memory push kernel"
+E2E_HEAD_GROUPS = 6   # head groups of the pipelined host-buffer call (4 heads each at H=24)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dense kernel: the ncu capture
 # summarised in profiles/ measured 384.8 MB at L=16,384, H=24 (algorithmic 402.7 MB; part of the
 # output was still in L2 at kernel end); traffic grows with L*H, so per row of one head:
@@ -127,7 +129,8 @@ def workload_config(n):
     return {"workload": "dense joint video+audio attention, one 5 s 864x480 DiT block: "
                         "L=52352 (512 audio + 51840 video), H=24, D=128, bf16, scale 1/sqrt(128), no mask",
             "sequence": SEQ, "heads": HEADS, "head_dim": DIM,
-            "parallelism": "single GPU" if n == 1 else "ulysses sp%d (head-scatter/sequence-gather all-to-all)" % n,
+            "parallelism": "single GPU" if n == 1 else "ulysses sp%d (head-scatter/sequence-gather all-to-all, %s)"
+                           % (n, EXCHANGE_NOTE),
             "l2": "inputs (965 MB) larger than L2 (126 MB); no flush between steps"}
 
 
@@ -139,10 +142,15 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="dense", choices=["dense", "vsa", "live"])
     parser.add_argument("--no-also", action="store_true", help="skip the secondary measurements")
+    parser.add_argument("--exchange", default="push", choices=["push", "nccl"],
+                        help="N>1: fused peer-memory exchange kernel (default) or transpose + NCCL send/recv")
     parser.add_argument("--sequence", type=int, default=0, help="override L (profiling on small cases)")
     parser.add_argument("--heads", type=int, default=0, help="override H (profiling on small cases)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    global EXCHANGE_NOTE
+    if args.exchange == "nccl":
+        EXCHANGE_NOTE = "transpose kernel + NCCL send/recv"
     if args.impl == "reference":
         return run_reference(args)
 
@@ -243,6 +251,22 @@ def main():
         tscr = wrap(scratch)
         tw = [wrap(w) for w in work]
 
+    exchange, slots = None, None
+    if world > 1 and args.exchange == "push":
+        # windows of four tensors (Q, K, V, gathered O) per rank, handles all-gathered through torch
+        xh = C.c_void_p()
+        handle = (C.c_ubyte * 64)()
+        if not lib.h3b_exchange_create(gpu.gpu, rank, world, shard_elems, 4, C.byref(xh), handle):
+            raise RuntimeError(gpu.error())
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device=device)
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        if not lib.h3b_exchange_connect(xh, bytes(torch.cat(everyone).cpu().tolist())):
+            raise RuntimeError(gpu.error())
+        exchange = xh
+        slots = [C.c_void_p(lib.h3b_exchange_slot(xh, i)) for i in range(4)]
+        dist.barrier()
+
     launches = [0]
 
     def attention_step():
@@ -251,7 +275,17 @@ def main():
             gpu.call("sdpa_bf16", to, tq, tk, tv, SEQ, HEADS, DIM, SCALE)
             launches[0] += 1
             return
-        # the exchange is in place, so each step scatters a fresh copy of the row shards
+        if exchange is not None:
+            # one kernel per exchange: local tensor -> final layout in the owners' windows
+            for i, t in enumerate((tq, tk, tv)):
+                if not lib.h3b_exchange_scatter_heads_bf16(exchange, i, t, rows, HEADS, DIM):
+                    raise RuntimeError(gpu.error())
+            gpu.call("sdpa_bf16", to, slots[0], slots[1], slots[2], SEQ, local_heads, DIM, SCALE)
+            if not lib.h3b_exchange_gather_heads_bf16(exchange, 3, to, rows, HEADS, DIM):
+                raise RuntimeError(gpu.error())
+            launches[0] += 5
+            return
+        # the NCCL exchange is in place, so each step scatters a fresh copy of the row shards
         for w, src in zip(work, (dq, dk, dv)):
             w.copy_(src, non_blocking=True)
         for t in tw:
@@ -262,10 +296,22 @@ def main():
 
     def e2e_step():
         """The same step through the public API with host buffers."""
+        if world == 1:
+            # one call: copy-in, kernel and copy-out pipelined over head groups
+            if not lib.h3b_sdpa_bf16_host(gpu.gpu, host_o.data_ptr(), host_q.data_ptr(), host_k.data_ptr(),
+                                          host_v.data_ptr(), SEQ, HEADS, DIM, SCALE, E2E_HEAD_GROUPS):
+                raise RuntimeError(gpu.error())
+            launches[0] += E2E_HEAD_GROUPS
+            return
         dq.copy_(host_q, non_blocking=True)
         dk.copy_(host_k, non_blocking=True)
         dv.copy_(host_v, non_blocking=True)
         attention_step()
+        if exchange is not None:
+            # the gathered output lives in window slot 3
+            if not lib.h3_gpu_download(gpu.gpu, slots[3], 0, host_o.data_ptr(), shard_elems * 2):
+                raise RuntimeError(gpu.error())
+            return
         host_o.copy_(do, non_blocking=True)
         stream.synchronize()
 
@@ -297,7 +343,8 @@ def main():
         torch.cuda.synchronize()
         start.record(stream)
         for _ in range(args.steps):
-            gpu.call("sdpa_bf16", to, tw[0], tw[1], tw[2], SEQ, local_heads, DIM, SCALE)
+            src = slots if exchange is not None else tw
+            gpu.call("sdpa_bf16", to, src[0], src[1], src[2], SEQ, local_heads, DIM, SCALE)
         stop.record(stream)
         torch.cuda.synchronize()
         return start.elapsed_time(stop) / args.steps
@@ -323,7 +370,9 @@ def main():
                      "flops_per_launch": kernel_flops,
                      "traffic": DENSE_TRAFFIC_BYTES_PER_ROW_HEAD * SEQ * HEADS / world},
         "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": 3 * shard_elems * 2, "d2h_bytes_per_step": shard_elems * 2},
+                "h2d_bytes_per_step": 3 * shard_elems * 2, "d2h_bytes_per_step": shard_elems * 2,
+                "api": "h3b_sdpa_bf16_host (pinned host buffers, %d pipelined head groups)" % E2E_HEAD_GROUPS
+                       if world == 1 else "pinned copies + ulysses scatter/sdpa/gather primitives"},
         "gpu_launches": counted,
         "clocks": clocks,
     }
@@ -343,6 +392,10 @@ def main():
         line.setdefault("also", {})["dit_step"] = dit
     if rank == 0:
         print(json.dumps(line), flush=True)
+    if exchange is not None:
+        torch.cuda.synchronize()
+        dist.barrier()
+        lib.h3b_exchange_free(exchange)
     if comm is not None:
         lib.h3_gpu_comm_free(comm)
     gpu.close()

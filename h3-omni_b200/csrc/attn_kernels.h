@@ -47,4 +47,10 @@ cudaError_t vsa_untile_merge(void *output, const void *tiled, const void *gate,
 cudaError_t swap_leading_16b(void *out, const void *in, unsigned a, unsigned b, size_t c_units,
                              cudaStream_t stream);
 
+// Fused transpose + all-to-all over peer memory (ulysses.cu). window[p] / flags[p] are this
+// process's mappings of rank p's window slot and flag array.
+cudaError_t exchange_push(bool gather, const void *src, void *const window[], unsigned long long *const flags[],
+                          unsigned long long epoch, unsigned *done_counter, int *status, int rank, int ranks,
+                          unsigned rows, unsigned heads, unsigned dim, cudaStream_t stream);
+
 }  // namespace h3b

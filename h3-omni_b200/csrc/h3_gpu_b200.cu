@@ -97,10 +97,20 @@ extern "C" cudaError_t h3b_device_status(int *status, int reset) {
 
 // ======================= 2. context and tensors =======================
 
+// Staging for h3b_sdpa_bf16_host: two slots of compact per-head-group device buffers,
+// a stream for each copy direction and the events that order the three streams.
+struct host_pipeline {
+    void *slot[2][4]{};            // q, k, v, out per slot
+    size_t slot_bytes{};
+    cudaStream_t h2d{}, d2h{};
+    cudaEvent_t loaded[2]{}, computed[2]{}, stored[2]{};
+    bool ready{};
+};
 struct h3_gpu {
     int device{};
     cudaStream_t own_stream{}, stream{};
     char error[512]{};
+    host_pipeline pipe;
 };
 struct h3_gpu_tensor {
     void *data{};
@@ -181,9 +191,29 @@ extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
     g->stream = g->own_stream;
     return g;
 }
+static void pipeline_release(h3_gpu *g) {
+    host_pipeline &p = g->pipe;
+    if (!p.ready) return;
+    cudaStreamSynchronize(p.h2d);
+    cudaStreamSynchronize(p.d2h);
+    for (auto &slot : p.slot)
+        for (void *&buffer : slot) {
+            if (buffer) cudaFree(buffer);
+            buffer = nullptr;
+        }
+    for (int s = 0; s < 2; s++) {
+        cudaEventDestroy(p.loaded[s]);
+        cudaEventDestroy(p.computed[s]);
+        cudaEventDestroy(p.stored[s]);
+    }
+    cudaStreamDestroy(p.h2d);
+    cudaStreamDestroy(p.d2h);
+    p = host_pipeline{};
+}
 extern "C" void h3_gpu_free(h3_gpu *g) {
     if (!g) return;
     cudaStreamSynchronize(g->stream);
+    pipeline_release(g);
     cudaStreamDestroy(g->own_stream);
     delete g;
 }
@@ -388,6 +418,85 @@ extern "C" int h3_gpu_cross_attention_bf16(h3_gpu *g, h3_gpu_tensor *y, size_t y
                                            static_cast<const uint16_t *>(k->data) + ko * width,
                                            static_cast<const uint16_t *>(v->data) + ko * width,
                                            nullptr, nq, nk, heads, 1.0f / sqrtf(128.0f), g->stream));
+}
+
+// Dense attention straight from and to host memory (an addition; the reference has no
+// host-buffer attention call). The heads are independent, so the work is cut into head groups
+// and pipelined over three streams: while group g is computed, group g+1 is copied in and
+// group g-1 is copied out. Host tensors are token-major [sequence][heads][128]; each group's
+// strided slice is packed into a compact device buffer by a 2-D copy, so the kernel sees a
+// plain [sequence][heads/groups][128] tensor. With pinned host memory the copies overlap the
+// kernel and the call costs about max(copy time, kernel time) instead of their sum; with
+// pageable memory it still works but the copies serialise. Returns after `out` is complete.
+static int pipeline_prepare(h3_gpu *g, size_t slot_bytes) {
+    host_pipeline &p = g->pipe;
+    if (p.ready && p.slot_bytes >= slot_bytes) return 1;
+    pipeline_release(g);
+    if (!cuda_ok(g, cudaStreamCreateWithFlags(&p.h2d, cudaStreamNonBlocking)) ||
+        !cuda_ok(g, cudaStreamCreateWithFlags(&p.d2h, cudaStreamNonBlocking)))
+        return 0;
+    for (int s = 0; s < 2; s++) {
+        if (!cuda_ok(g, cudaEventCreateWithFlags(&p.loaded[s], cudaEventDisableTiming)) ||
+            !cuda_ok(g, cudaEventCreateWithFlags(&p.computed[s], cudaEventDisableTiming)) ||
+            !cuda_ok(g, cudaEventCreateWithFlags(&p.stored[s], cudaEventDisableTiming)))
+            return 0;
+        for (int t = 0; t < 4; t++)
+            if (!cuda_ok(g, cudaMalloc(&p.slot[s][t], slot_bytes))) return 0;
+    }
+    p.slot_bytes = slot_bytes;
+    p.ready = true;
+    return 1;
+}
+extern "C" int h3b_sdpa_bf16_host(h3_gpu *g, uint16_t *out, const uint16_t *q, const uint16_t *k,
+                                  const uint16_t *v, uint32_t sequence, uint32_t heads,
+                                  uint32_t head_dim, float scale, uint32_t head_groups) {
+    if (!g) return 0;
+    if (!out || !q || !k || !v || !sequence || !heads) {
+        set_error(g, "host attention: null pointer or empty shape");
+        return 0;
+    }
+    if (head_dim != 128) {
+        set_error(g, "BF16 attention supports head dimension 128 only");
+        return 0;
+    }
+    if (!head_groups || heads % head_groups) {
+        set_error(g, "host attention: %u heads do not split into %u groups", heads, head_groups);
+        return 0;
+    }
+    const uint32_t hg = heads / head_groups;
+    const size_t row_bytes = (size_t)hg * 256, pitch = (size_t)heads * 256;
+    if (!pipeline_prepare(g, row_bytes * sequence)) return 0;
+    host_pipeline &p = g->pipe;
+    // everything already queued on the context's stream comes first
+    if (!cuda_ok(g, cudaEventRecord(p.computed[0], g->stream)) ||
+        !cuda_ok(g, cudaStreamWaitEvent(p.h2d, p.computed[0], 0)))
+        return 0;
+    for (uint32_t group = 0; group < head_groups; group++) {
+        const int s = group & 1;
+        const size_t offset = (size_t)group * hg * 128;   // elements into a host row
+        if (group >= 2) {
+            // slot reuse: inputs after the kernel of group-2, output after its copy-out
+            if (!cuda_ok(g, cudaStreamWaitEvent(p.h2d, p.computed[s], 0)) ||
+                !cuda_ok(g, cudaStreamWaitEvent(g->stream, p.stored[s], 0)))
+                return 0;
+        }
+        const uint16_t *src[3] = {q, k, v};
+        for (int t = 0; t < 3; t++)
+            if (!cuda_ok(g, cudaMemcpy2DAsync(p.slot[s][t], row_bytes, src[t] + offset, pitch,
+                                              row_bytes, sequence, cudaMemcpyHostToDevice, p.h2d)))
+                return 0;
+        if (!cuda_ok(g, cudaEventRecord(p.loaded[s], p.h2d)) ||
+            !cuda_ok(g, cudaStreamWaitEvent(g->stream, p.loaded[s], 0)) ||
+            !cuda_ok(g, h3_flash3_bf16(p.slot[s][3], p.slot[s][0], p.slot[s][1], p.slot[s][2], nullptr,
+                                       1, sequence, hg, hg, scale, g->stream)) ||
+            !cuda_ok(g, cudaEventRecord(p.computed[s], g->stream)) ||
+            !cuda_ok(g, cudaStreamWaitEvent(p.d2h, p.computed[s], 0)) ||
+            !cuda_ok(g, cudaMemcpy2DAsync(out + offset, pitch, p.slot[s][3], row_bytes, row_bytes,
+                                          sequence, cudaMemcpyDeviceToHost, p.d2h)) ||
+            !cuda_ok(g, cudaEventRecord(p.stored[s], p.d2h)))
+            return 0;
+    }
+    return cuda_ok(g, cudaStreamSynchronize(p.d2h)) && cuda_ok(g, cudaStreamSynchronize(g->stream));
 }
 
 // ======================= video sparse attention =======================
@@ -689,4 +798,116 @@ extern "C" int h3_gpu_all_gather_bf16(h3_gpu *g, h3_gpu_comm *c, h3_gpu_tensor *
         return 0;
     return nccl_ok(g, ncclAllGather(input->data, output->data, count * 2, ncclUint8, c->comm,
                                     g->stream), "all-gather");
+}
+
+// ======================= fused Ulysses exchange over peer memory =======================
+// One process per GPU: each rank owns a window (cudaMalloc, exported as a CUDA IPC handle) of
+// `slots` tensors plus a flag array; after h3b_exchange_connect every rank holds mappings of
+// all windows and an exchange is one kernel (csrc/ulysses.cu) instead of a transpose kernel
+// plus NCCL send/recv. No counterpart in the reference, which exchanges through NCCL only.
+struct h3b_exchange {
+    h3_gpu *gpu{};
+    int rank{}, ranks{}, slots{};
+    size_t slot_elements{}, slot_bytes{}, flags_offset{};
+    char *local{};                       // this rank's window
+    char *mapped[16]{};                  // every rank's window as seen from here
+    unsigned *done_counter{};            // in the local window, after the flags
+    unsigned long long epoch{};
+    bool connected{};
+};
+
+extern "C" void h3b_exchange_free(h3b_exchange *x) {
+    if (!x) return;
+    cudaStreamSynchronize(x->gpu->stream);
+    for (int p = 0; p < x->ranks; p++)
+        if (p != x->rank && x->mapped[p]) cudaIpcCloseMemHandle(x->mapped[p]);
+    if (x->local) cudaFree(x->local);
+    delete x;
+}
+
+extern "C" int h3b_exchange_create(h3_gpu *g, int rank, int ranks, size_t slot_elements, int slots,
+                                   h3b_exchange **exchange, void *handle64) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    if (!g || !exchange || !handle64 || ranks < 1 || ranks > 16 || rank < 0 || rank >= ranks ||
+        slots < 1 || !slot_elements) {
+        set_error(g, "exchange: invalid rank %d of %d or empty window", rank, ranks);
+        return 0;
+    }
+    auto *x = new (std::nothrow) h3b_exchange{};
+    if (!x) return 0;
+    x->gpu = g;
+    x->rank = rank;
+    x->ranks = ranks;
+    x->slots = slots;
+    x->slot_elements = slot_elements;
+    x->slot_bytes = (slot_elements * 2 + 255) / 256 * 256;
+    x->flags_offset = x->slot_bytes * slots;
+    const size_t bytes = x->flags_offset + 16 * sizeof(unsigned long long) + 256;
+    cudaIpcMemHandle_t handle;
+    if (!cuda_ok(g, cudaMalloc(reinterpret_cast<void **>(&x->local), bytes)) ||
+        !cuda_ok(g, cudaMemset(x->local, 0, bytes)) ||
+        !cuda_ok(g, cudaIpcGetMemHandle(&handle, x->local))) {
+        h3b_exchange_free(x);
+        return 0;
+    }
+    x->done_counter = reinterpret_cast<unsigned *>(x->local + x->flags_offset + 16 * sizeof(unsigned long long));
+    x->mapped[rank] = x->local;
+    memcpy(handle64, &handle, 64);
+    *exchange = x;
+    return 1;
+}
+
+// handles: ranks x 64 bytes in rank order (every rank's handle64, gathered by any transport).
+extern "C" int h3b_exchange_connect(h3b_exchange *x, const void *handles) {
+    if (!x || !handles) return 0;
+    h3_gpu *g = x->gpu;
+    for (int p = 0; p < x->ranks; p++) {
+        if (p == x->rank) continue;
+        cudaIpcMemHandle_t handle;
+        memcpy(&handle, static_cast<const char *>(handles) + 64 * p, 64);
+        void *mapped = nullptr;
+        if (!cuda_ok(g, cudaIpcOpenMemHandle(&mapped, handle, cudaIpcMemLazyEnablePeerAccess))) return 0;
+        x->mapped[p] = static_cast<char *>(mapped);
+    }
+    x->connected = true;
+    return 1;
+}
+
+// Non-owning tensor over slot `slot` of this rank's window (free it with h3_gpu_tensor_free).
+extern "C" h3_gpu_tensor *h3b_exchange_slot(h3b_exchange *x, int slot) {
+    if (!x || slot < 0 || slot >= x->slots) return nullptr;
+    return h3b_tensor_wrap(x->gpu, x->local + x->slot_bytes * slot, x->slot_elements, H3_GPU_BF16);
+}
+
+static int exchange_run(h3b_exchange *x, bool gather, int slot, const h3_gpu_tensor *src, uint32_t rows,
+                        uint32_t heads, uint32_t dim) {
+    if (!x) return 0;
+    h3_gpu *g = x->gpu;
+    const size_t count = (size_t)rows * heads * dim;
+    if (!x->connected || slot < 0 || slot >= x->slots || heads % x->ranks || count > x->slot_elements) {
+        set_error(g, "exchange: not connected, bad slot, %u heads over %d ranks, or %zu elements exceed the slot",
+                  heads, x->ranks, count);
+        return 0;
+    }
+    if (!require_bf16(g, src, count, "exchange source")) return 0;
+    void *window[16];
+    unsigned long long *flags[16];
+    for (int p = 0; p < x->ranks; p++) {
+        window[p] = x->mapped[p] + x->slot_bytes * slot;
+        flags[p] = reinterpret_cast<unsigned long long *>(x->mapped[p] + x->flags_offset);
+    }
+    int *status = nullptr;
+    if (!cuda_ok(g, h3b::device_status_word(&status))) return 0;
+    return cuda_ok(g, h3b::exchange_push(gather, src->data, window, flags, ++x->epoch, x->done_counter, status,
+                                         x->rank, x->ranks, rows, heads, dim, g->stream));
+}
+// src [rows][heads][dim] on each rank -> slot of every rank: [ranks*rows][heads/ranks][dim].
+extern "C" int h3b_exchange_scatter_heads_bf16(h3b_exchange *x, int slot, const h3_gpu_tensor *src,
+                                               uint32_t rows, uint32_t heads, uint32_t dim) {
+    return exchange_run(x, false, slot, src, rows, heads, dim);
+}
+// src [ranks*rows][heads/ranks][dim] on each rank -> slot of every rank: [rows][heads][dim].
+extern "C" int h3b_exchange_gather_heads_bf16(h3b_exchange *x, int slot, const h3_gpu_tensor *src,
+                                              uint32_t rows, uint32_t heads, uint32_t dim) {
+    return exchange_run(x, true, slot, src, rows, heads, dim);
 }

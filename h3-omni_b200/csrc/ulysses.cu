@@ -38,3 +38,120 @@ cudaError_t swap_leading_16b(void *out, const void *in, unsigned a, unsigned b, 
     return cudaGetLastError();
 }
 }  // namespace h3b
+
+// ---- fused exchange over peer memory -------------------------------------------------
+// The NCCL path above is transpose kernel + grouped send/recv (+ the same in reverse): two
+// passes over the tensor per exchange. Here one kernel reads the local tensor once and stores
+// every 16-byte unit straight to its final place in the owning rank's window over NVLink
+// (plain peer stores, no TMA), then the last CTA to finish publishes this rank's epoch to every
+// peer and waits - bounded - until every peer's epoch has arrived here.
+//   scatter: src [rows][heads][dim] -> window of rank p gets [ranks*rows][heads/ranks][dim]
+//   gather : src [ranks*rows][heads/ranks][dim] -> window of rank p gets [rows][heads][dim]
+namespace h3b {
+namespace {
+
+constexpr int MAX_RANKS = 16;
+struct PushArgs {
+    uint4 *window[MAX_RANKS];                 // slot base in every rank's window (peer pointers)
+    unsigned long long *flags[MAX_RANKS];     // flag array [ranks] in every rank's window
+    unsigned long long epoch;
+    unsigned *done_counter;                   // local
+    int *status;                              // local device status word
+    int rank, ranks;
+    unsigned rows, heads, dim16;              // dim in 16-byte units
+};
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+template <bool GATHER>
+__global__ void __launch_bounds__(256)
+exchange_push_kernel(const uint4 *__restrict__ src, PushArgs a) {
+    const unsigned hg = a.heads / a.ranks;
+    const size_t total = (size_t)(GATHER ? a.ranks : 1) * a.rows * (GATHER ? hg : a.heads) * a.dim16;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const unsigned d = (unsigned)(i % a.dim16);
+        size_t rest = i / a.dim16;
+        if (!GATHER) {
+            // src (row, head): head group p goes to rank p at row rank*rows + row
+            const unsigned head = (unsigned)(rest % a.heads), row = (unsigned)(rest / a.heads);
+            const unsigned peer = head / hg;
+            a.window[peer][(((size_t)a.rank * a.rows + row) * hg + head % hg) * a.dim16 + d] = src[i];
+        } else {
+            // src (global row, local head): rows of rank p go to rank p at head rank*hg + head
+            const unsigned head = (unsigned)(rest % hg);
+            const size_t grow = rest / hg;
+            const unsigned peer = (unsigned)(grow / a.rows), row = (unsigned)(grow % a.rows);
+            a.window[peer][(((size_t)row) * a.heads + (size_t)a.rank * hg + head) * a.dim16 + d] = src[i];
+        }
+    }
+    // completion: the last CTA publishes and waits
+    __shared__ bool last;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(a.done_counter, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!last) return;
+    if (threadIdx.x == 0) *a.done_counter = 0;   // ready for the next exchange on this stream
+    if ((int)threadIdx.x < a.ranks) {
+        const int peer = threadIdx.x;
+        st_release_sys(a.flags[peer] + a.rank, a.epoch);
+        // wait for peer's data to be in our window: its flag entry here reaches the epoch
+        const unsigned long long *mine = a.flags[a.rank] + peer;
+        const unsigned long long start = clock64();
+        bool ok = false;
+        for (unsigned spin = 0;; spin++) {
+            if (ld_acquire_sys(mine) >= a.epoch) {
+                ok = true;
+                break;
+            }
+            if ((spin & 1023u) == 1023u && clock64() - start > 4000000000ull) break;   // ~2 s
+            __nanosleep(100);
+        }
+        if (!ok) atomicCAS(a.status, 0, 1);   // wait timed out; the host sees status 1
+    }
+}
+
+}  // namespace
+
+cudaError_t exchange_push(bool gather, const void *src, void *const window[], unsigned long long *const flags[],
+                          unsigned long long epoch, unsigned *done_counter, int *status, int rank, int ranks,
+                          unsigned rows, unsigned heads, unsigned dim, cudaStream_t stream) {
+    if (ranks < 1 || ranks > MAX_RANKS || heads % ranks || (dim * 2) % 16) return cudaErrorInvalidValue;
+    PushArgs a{};
+    for (int p = 0; p < ranks; p++) {
+        a.window[p] = static_cast<uint4 *>(window[p]);
+        a.flags[p] = flags[p];
+    }
+    a.epoch = epoch;
+    a.done_counter = done_counter;
+    a.status = status;
+    a.rank = rank;
+    a.ranks = ranks;
+    a.rows = rows;
+    a.heads = heads;
+    a.dim16 = dim * 2 / 16;
+    static thread_local int sms = 0;
+    if (!sms) {
+        int device = 0;
+        cudaError_t e = cudaGetDevice(&device);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (e != cudaSuccess) return e;
+    }
+    const size_t total = (size_t)rows * heads * a.dim16;
+    const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, (size_t)sms * 4);
+    if (gather)
+        exchange_push_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const uint4 *>(src), a);
+    else
+        exchange_push_kernel<false><<<blocks, 256, 0, stream>>>(static_cast<const uint4 *>(src), a);
+    return cudaGetLastError();
+}
+
+}  // namespace h3b

@@ -172,6 +172,15 @@ void *h3b_tensor_data(const h3_gpu_tensor *tensor);
 int h3b_gpu_set_stream(h3_gpu *gpu, cudaStream_t stream);
 cudaStream_t h3b_gpu_stream(const h3_gpu *gpu);
 
+/* Dense attention from and to HOST memory, head dim 128: q, k, v, out are token-major
+ * [sequence][heads][128] bf16 in host memory (pinned for full speed). The heads are cut into
+ * head_groups groups (heads % head_groups == 0) and copy-in, kernel and copy-out of
+ * consecutive groups overlap on three streams, so the call costs about
+ * max(copy time, kernel time). Synchronous: returns when `out` is complete. */
+int h3b_sdpa_bf16_host(h3_gpu *gpu, uint16_t *out, const uint16_t *q, const uint16_t *k,
+                       const uint16_t *v, uint32_t sequence, uint32_t heads, uint32_t head_dim,
+                       float scale, uint32_t head_groups);
+
 /* One-process-per-GPU communicator: rank 0 calls h3b_comm_unique_id, ships the 128 bytes
  * to the other ranks by any means, then every rank calls h3b_comm_init_rank. */
 int h3b_comm_unique_id(void *id128, char *error, size_t error_size);
@@ -179,6 +188,27 @@ int h3b_comm_init_rank(const void *id128, int rank, int count, h3_gpu_comm **com
                        size_t error_size);
 int h3b_comm_rank(const h3_gpu_comm *comm);
 int h3b_comm_size(const h3_gpu_comm *comm);
+
+/* Fused Ulysses exchange over peer memory, one process per GPU. Every rank creates a window of
+ * `slots` bf16 tensors of slot_elements each and gets a 64-byte handle; the ranks all-gather the
+ * handles by any transport and connect. A scatter or gather is then ONE kernel that reads the
+ * local tensor once and stores each 16-byte unit into its final place in the owning rank's window
+ * over NVLink, followed by a bounded epoch handshake (a timeout is reported through the device
+ * status word, not a hang). The destination of both calls is slot `slot` of every rank's window:
+ *   scatter: src [rows][heads][dim] per rank -> [ranks*rows][heads/ranks][dim] per rank
+ *   gather : src [ranks*rows][heads/ranks][dim] per rank -> [rows][heads][dim] per rank
+ * Calls must be made in the same order on every rank, on the context's stream; a slot must not
+ * be overwritten before its readers on that rank were enqueued on the same stream. */
+typedef struct h3b_exchange h3b_exchange;
+int h3b_exchange_create(h3_gpu *gpu, int rank, int ranks, size_t slot_elements, int slots,
+                        h3b_exchange **exchange, void *handle64);
+int h3b_exchange_connect(h3b_exchange *exchange, const void *handles);
+void h3b_exchange_free(h3b_exchange *exchange);
+h3_gpu_tensor *h3b_exchange_slot(h3b_exchange *exchange, int slot);
+int h3b_exchange_scatter_heads_bf16(h3b_exchange *exchange, int slot, const h3_gpu_tensor *src,
+                                    uint32_t rows, uint32_t heads, uint32_t dim);
+int h3b_exchange_gather_heads_bf16(h3b_exchange *exchange, int slot, const h3_gpu_tensor *src,
+                                   uint32_t rows, uint32_t heads, uint32_t dim);
 
 /* VSA introspection for tests and tools: geometry, an override for the number of kept
  * video tiles (the reference fixes ceil(10 %)), and device pointers of the work buffers

@@ -219,3 +219,27 @@ def test_run_twice_is_deterministic(gpu, oracle):
         gpu.call("sdpa_bf16", ty, tq, tk, tv, L, H, 128, SCALE)
         outs.append(gpu.read(ty, q.shape))
     assert np.array_equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("groups", [1, 2, 4])
+def test_host_buffer_attention_matches_device_path(gpu, oracle, groups):
+    """h3b_sdpa_bf16_host (head groups pipelined over copy and compute streams, pageable host
+    memory here) gives the same bits as the device-tensor primitive: grouping heads changes
+    nothing per head. A second call reuses the staging slots."""
+    L, H = 700, 8
+    q, k, v = (oracle.normal_bf16((L, H, 128), 90 + i) for i in range(3))
+    ty = gpu.empty_bf16(q.size)
+    gpu.call("sdpa_bf16", ty, gpu.tensor(q), gpu.tensor(k), gpu.tensor(v), L, H, 128, SCALE)
+    want = gpu.read(ty, q.shape)
+    for _ in range(2):
+        out = np.zeros(q.shape, dtype=np.uint16)
+        ok = gpu.lib.h3b_sdpa_bf16_host(gpu.gpu, out.ctypes.data_as(C.c_void_p), q.ctypes.data_as(C.c_void_p),
+                                        k.ctypes.data_as(C.c_void_p), v.ctypes.data_as(C.c_void_p), L, H,
+                                        128, SCALE, groups)
+        assert ok, gpu.error()
+        assert np.array_equal(out, want)
+    assert not gpu.lib.h3b_sdpa_bf16_host(gpu.gpu, out.ctypes.data_as(C.c_void_p), q.ctypes.data_as(C.c_void_p),
+                                          k.ctypes.data_as(C.c_void_p), v.ctypes.data_as(C.c_void_p), L, H,
+                                          128, SCALE, 3)
+    assert "do not split into 3 groups" in gpu.error()
+    assert gpu.device_status() == 0

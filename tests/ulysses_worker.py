@@ -79,6 +79,39 @@ def main():
     gpu.call("all_gather_bf16", comm, total, src, rows * H * D)
     assert np.array_equal(gpu.read(total, (world, rows, H, D)), shards[0])
     assert gpu.device_status() == 0
+
+    # ---- the fused exchange over peer memory must move the same bytes as the NCCL path ----
+    x = C.c_void_p()
+    handle = (C.c_ubyte * 64)()
+    assert lib.h3b_exchange_create(gpu.gpu, rank, world, rows * H * D, 4, C.byref(x), handle), gpu.error()
+    tmp = rdv / ("ipc_%d.tmp" % rank)
+    tmp.write_bytes(bytes(handle))
+    tmp.rename(rdv / ("ipc_%d" % rank))
+    deadline = time.time() + 120
+    while not all((rdv / ("ipc_%d" % r)).exists() for r in range(world)):
+        if time.time() > deadline:
+            raise SystemExit("handle rendezvous timed out")
+        time.sleep(0.05)
+    handles = b"".join((rdv / ("ipc_%d" % r)).read_bytes() for r in range(world))
+    assert lib.h3b_exchange_connect(x, handles), gpu.error()
+    slots = [lib.h3b_exchange_slot(x, i) for i in range(4)]
+    for epoch in range(2):   # twice: the epoch handshake must hold across repeated exchanges
+        for i, sh in enumerate(shards):
+            src = gpu.tensor(sh[rank])
+            assert lib.h3b_exchange_scatter_heads_bf16(x, i, src, rows, H, D), gpu.error()
+            got = gpu.read(slots[i], (world * rows, H // world, D))
+            assert np.array_equal(got, oracle.ulysses(sh)[rank]), "fused scatter mismatch"
+        out2 = gpu.empty_bf16(rows * H * D)
+        gpu.call("zero", out2)
+        gpu.call("sdpa_bf16", out2, slots[0], slots[1], slots[2], L, plan.local_heads, D, scale)
+        assert np.array_equal(gpu.read(out2, (world * rows, H // world, D))[:L], local[:L])
+        assert lib.h3b_exchange_gather_heads_bf16(x, 3, out2, rows, H, D), gpu.error()
+        fused = gpu.read(slots[3], (rows, H, D))
+        assert np.array_equal(fused[:n], gathered[:n]), "fused gather differs from the NCCL gather"
+        assert gpu.device_status() == 0
+    for t in slots:
+        lib.h3_gpu_tensor_free(t)
+    lib.h3b_exchange_free(x)
     lib.h3_gpu_comm_free(comm)
     gpu.close()
     print("OK rank %d" % rank, flush=True)
