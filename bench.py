@@ -363,7 +363,7 @@ def main():
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(world),
-        "roofline": {"bound": "tensor", "kernel": "attn_tc5_kernel<128,false>", "achieved": achieved,
+        "roofline": {"bound": "tensor", "kernel": "attn_tc5_pair_kernel", "achieved": achieved,
                      "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
                      "peak_source": pk["source"] + " burst", "frac_of_sustained": achieved / pk["tflops_sustained"],
                      "frac_of_nominal_2250": achieved / 2250.0, "kernel_ms": kernel_ms,
@@ -379,7 +379,8 @@ def main():
 
     dit = None
     if not args.no_also and not args.sequence:
-        dit = dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_over_ranks)
+        dit = dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_over_ranks,
+                       exchange=exchange, slots=slots)
     if rank == 0 and world == 1:
         oracle = entry.load_oracle()
         oracle.build()
@@ -403,7 +404,8 @@ def main():
         dist.destroy_process_group()
 
 
-def dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_over_ranks, blocks=50, steps=2):
+def dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_over_ranks, blocks=50, steps=2,
+             exchange=None, slots=None):
     """One denoising step of the 50-block DiT at the benchmark shape, timed at N GPUs.
 
     Op order of the reference's run_block (h3_dit.c:2450-2673) with the reference's widths
@@ -428,6 +430,7 @@ def dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_o
     wrap = lambda t: gpu.wrap(t.data_ptr(), t.numel())
     tq, tk, tv, to, tscr = wrap(q), wrap(k), wrap(v), wrap(o), wrap(scratch)
     F = torch.nn.functional
+    lib = gpu.lib
 
     def norm_mod(x, scale, shift):
         return F.rms_norm(x, (hidden,)) * (1 + scale) + shift
@@ -440,12 +443,21 @@ def dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_o
             q.copy_(F.rms_norm(qkv[:, 0], (DIM,)))       # stands in for QK-RMS + RoPE writing Q, K, V
             k.copy_(F.rms_norm(qkv[:, 1], (DIM,)))
             v.copy_(qkv[:, 2])
-            if world > 1:
-                for t in (tq, tk, tv):
-                    gpu.call("ulysses_scatter_heads_bf16", comm, t, tscr, rows, HEADS, DIM)
-            gpu.call("sdpa_bf16", to, tq, tk, tv, plan.sequence, local_heads, DIM, SCALE)
-            if world > 1:
-                gpu.call("ulysses_gather_heads_bf16", comm, to, tscr, rows, HEADS, DIM)
+            if exchange is not None:
+                for i, t in enumerate((tq, tk, tv)):
+                    if not lib.h3b_exchange_scatter_heads_bf16(exchange, i, t, rows, HEADS, DIM):
+                        raise RuntimeError(gpu.error())
+                gpu.call("sdpa_bf16", tscr, slots[0], slots[1], slots[2], plan.sequence, local_heads, DIM, SCALE)
+                if not lib.h3b_exchange_gather_heads_bf16(exchange, 3, tscr, rows, HEADS, DIM):
+                    raise RuntimeError(gpu.error())
+                gpu.call("copy_bf16", to, 0, slots[3], 0, rows * HEADS * DIM)   # window -> torch tensor
+            else:
+                if world > 1:
+                    for t in (tq, tk, tv):
+                        gpu.call("ulysses_scatter_heads_bf16", comm, t, tscr, rows, HEADS, DIM)
+                gpu.call("sdpa_bf16", to, tq, tk, tv, plan.sequence, local_heads, DIM, SCALE)
+                if world > 1:
+                    gpu.call("ulysses_gather_heads_bf16", comm, to, tscr, rows, HEADS, DIM)
             x = x + mod[2] * (o.view(rows, inner) @ w_out)
             h = norm_mod(x, mod[3], mod[4])
             u = h @ w_fc1

@@ -75,23 +75,31 @@ __global__ void __launch_bounds__(256)
 exchange_push_kernel(const uint4 *__restrict__ src, PushArgs a) {
     const unsigned hg = a.heads / a.ranks;
     const size_t total = (size_t)(GATHER ? a.ranks : 1) * a.rows * (GATHER ? hg : a.heads) * a.dim16;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (size_t)gridDim.x * blockDim.x) {
+    auto destination = [&](size_t i) -> uint4 * {
         const unsigned d = (unsigned)(i % a.dim16);
-        size_t rest = i / a.dim16;
+        const size_t rest = i / a.dim16;
         if (!GATHER) {
             // src (row, head): head group p goes to rank p at row rank*rows + row
             const unsigned head = (unsigned)(rest % a.heads), row = (unsigned)(rest / a.heads);
-            const unsigned peer = head / hg;
-            a.window[peer][(((size_t)a.rank * a.rows + row) * hg + head % hg) * a.dim16 + d] = src[i];
-        } else {
-            // src (global row, local head): rows of rank p go to rank p at head rank*hg + head
-            const unsigned head = (unsigned)(rest % hg);
-            const size_t grow = rest / hg;
-            const unsigned peer = (unsigned)(grow / a.rows), row = (unsigned)(grow % a.rows);
-            a.window[peer][(((size_t)row) * a.heads + (size_t)a.rank * hg + head) * a.dim16 + d] = src[i];
+            return a.window[head / hg] + (((size_t)a.rank * a.rows + row) * hg + head % hg) * a.dim16 + d;
         }
+        // src (global row, local head): rows of rank p go to rank p at head rank*hg + head
+        const unsigned head = (unsigned)(rest % hg);
+        const size_t grow = rest / hg;
+        const unsigned row = (unsigned)(grow % a.rows);
+        return a.window[grow / a.rows] + ((size_t)row * a.heads + (size_t)a.rank * hg + head) * a.dim16 + d;
+    };
+    // four independent 16-byte loads in flight per thread, then four (mostly remote) stores
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < total; i += 4 * stride) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) v[u] = __ldg(src + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < 4; u++) *destination(i + u * stride) = v[u];
     }
+    for (; i < total; i += stride) *destination(i) = __ldg(src + i);
     // completion: the last CTA publishes and waits
     __shared__ bool last;
     __threadfence_system();
@@ -146,7 +154,7 @@ cudaError_t exchange_push(bool gather, const void *src, void *const window[], un
         if (e != cudaSuccess) return e;
     }
     const size_t total = (size_t)rows * heads * a.dim16;
-    const unsigned blocks = (unsigned)std::min<size_t>((total + 255) / 256, (size_t)sms * 4);
+    const unsigned blocks = (unsigned)std::min<size_t>((total + 1023) / 1024, (size_t)sms * 8);
     if (gather)
         exchange_push_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const uint4 *>(src), a);
     else
