@@ -59,7 +59,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(device_index), "--query-gpu=" + self.FIELDS,
-                 "--format=csv,noheader,nounits", "-lms", "200"], stdout=self.file,
+                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.file,
                 stderr=subprocess.DEVNULL)
         except OSError:
             pass
@@ -329,11 +329,12 @@ def main():
         barrier()
         return max_over_ranks(start.elapsed_time(stop) / steps)
 
+    # Clocks are sampled from before the warm-up until after the end-to-end leg, so that short
+    # timed regions (a few milliseconds per step at 8 GPUs) still get samples under load.
     sampler = ClockSampler(local_rank) if rank == 0 else None
     launches[0] = 0
     ms = timed(attention_step, args.steps, args.warmup)
     counted = launches[0] * args.steps // (args.steps + args.warmup)
-    clocks = sampler.stop() if sampler else None
 
     # kernel-only duration of the dense kernel (the dominant kernel), events on its own stream
     def kernel_only():
@@ -351,6 +352,13 @@ def main():
 
     kernel_ms = kernel_only()
     e2e_ms = timed(e2e_step, max(2, args.steps // 2), 1)
+    if ms * (args.steps + args.warmup) < 1500.0:
+        # every rank keeps its device busy with the same step (ms is the max over ranks, so all
+        # ranks agree) until the sampler on rank 0 has seen about a second of load
+        for _ in range(int(1000.0 / max(ms, 0.05))):
+            attention_step()
+        barrier()
+    clocks = sampler.stop() if sampler else None
     status = gpu.device_status()
     if status:
         raise SystemExit("device status %d after the timed region" % status)
