@@ -30,7 +30,7 @@ import __graft_entry__ as entry  # noqa: E402
 SEQ_VIDEO, SEQ_AUDIO, HEADS, DIM = 51840, 512, 24, 128
 SEQ = SEQ_VIDEO + SEQ_AUDIO
 SCALE = float(1.0 / np.sqrt(128.0))
-EXCHANGE_NOTE = "fused peer-memory push kernel"
+EXCHANGE_NOTE = "fused peer-memory push kernels; gather fused into the attention epilogue"
 E2E_HEAD_GROUPS = 6   # head groups of the pipelined host-buffer call (4 heads each at H=24)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dense kernel: the ncu capture
 # summarised in profiles/ measured 384.8 MB at L=16,384, H=24 (algorithmic 402.7 MB; part of the
@@ -280,8 +280,9 @@ def main():
             for i, t in enumerate((tq, tk, tv)):
                 if not lib.h3b_exchange_scatter_heads_bf16(exchange, i, t, rows, HEADS, DIM):
                     raise RuntimeError(gpu.error())
-            gpu.call("sdpa_bf16", to, slots[0], slots[1], slots[2], SEQ, local_heads, DIM, SCALE)
-            if not lib.h3b_exchange_gather_heads_bf16(exchange, 3, to, rows, HEADS, DIM):
+            # attention stores each output row straight into its owner's window (slot 3)
+            if not lib.h3b_exchange_sdpa_gather_bf16(exchange, 3, slots[0], slots[1], slots[2], SEQ, rows,
+                                                     HEADS, SCALE):
                 raise RuntimeError(gpu.error())
             launches[0] += 5
             return

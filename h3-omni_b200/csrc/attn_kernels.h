@@ -10,15 +10,26 @@ namespace h3b {
 // Address of this device's status word (0 = ok; see DeviceStatus in sm100_ptx.cuh).
 cudaError_t device_status_word(int **word);
 
-// tcgen05 kernels (attn_tc5.cu). Token-major [B][L][H][128] bf16.
+// Output redirection for the sequence-gather fused into the attention epilogue: query row r of
+// local head h is stored to rank r / rows_per_rank, at [r % rows_per_rank][rank*local_heads + h]
+// of that rank's [rows_per_rank][total_heads][128] tensor (plain peer stores over NVLink).
+struct PeerOutput {
+    void *base[16];
+    unsigned rows_per_rank, rank, total_heads;
+};
+
+// tcgen05 kernels (attn_tc5.cu). Token-major [B][L][H][128] bf16. With `peer` (batch 1 only)
+// `out` is ignored and the output goes to the owners' tensors.
 cudaError_t attn_dense_tc5(void *out, const void *q, const void *k, const void *v, float *lse,
                            unsigned batch, unsigned lq, unsigned lk, unsigned heads,
-                           unsigned kv_heads, float scale, cudaStream_t stream);
+                           unsigned kv_heads, float scale, cudaStream_t stream,
+                           const PeerOutput *peer = nullptr);
 // Two query tiles per CTA (attn_tc5_pair.cu); tensor maps as built by attn_dense_tc5.
 cudaError_t attn_dense_tc5_pair(const ::CUtensorMap_st *mq, const ::CUtensorMap_st *mk,
                                 const ::CUtensorMap_st *mv, void *out, float *lse, unsigned batch,
                                 unsigned lq, unsigned lk, unsigned heads, unsigned kv_heads,
-                                float scale, int *status, cudaStream_t stream);
+                                float scale, int *status, cudaStream_t stream,
+                                const PeerOutput *peer = nullptr);
 // Head-major tiled [H][tiles*64][128] bf16 with per-(head, query tile) KV tile lists.
 cudaError_t attn_sparse_tc5(void *out, const void *q, const void *k, const void *v, float *lse,
                             const int *indices, const int *counts, const int *sizes,
@@ -49,6 +60,9 @@ cudaError_t swap_leading_16b(void *out, const void *in, unsigned a, unsigned b, 
 
 // Fused transpose + all-to-all over peer memory (ulysses.cu). window[p] / flags[p] are this
 // process's mappings of rank p's window slot and flag array.
+// Epoch handshake alone (after a kernel that stored into the peers' windows itself).
+cudaError_t exchange_handshake(unsigned long long *const flags[], unsigned long long epoch, int *status,
+                               int rank, int ranks, cudaStream_t stream);
 cudaError_t exchange_push(bool gather, const void *src, void *const window[], unsigned long long *const flags[],
                           unsigned long long epoch, unsigned *done_counter, int *status, int rank, int ranks,
                           unsigned rows, unsigned heads, unsigned dim, cudaStream_t stream);

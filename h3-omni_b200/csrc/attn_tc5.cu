@@ -455,7 +455,7 @@ cudaError_t launch(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorM
 
 cudaError_t attn_dense_tc5(void *out, const void *q, const void *k, const void *v, float *lse,
                            unsigned batch, unsigned lq, unsigned lk, unsigned heads,
-                           unsigned kv_heads, float scale, cudaStream_t stream) {
+                           unsigned kv_heads, float scale, cudaStream_t stream, const PeerOutput *peer) {
     if (!batch || !lq || !lk || !heads || !kv_heads || heads % kv_heads) return cudaErrorInvalidValue;
     if (heads > 65535u || batch > 65535u) return cudaErrorInvalidValue;
     int *status = nullptr;
@@ -485,9 +485,9 @@ cudaError_t attn_dense_tc5(void *out, const void *q, const void *k, const void *
     p.lse = lse;
     p.status = status;
     // More than one query tile: the two-tile-per-CTA kernel (attn_tc5_pair.cu).
-    if (lq > (unsigned)BM)
+    if (lq > (unsigned)BM || peer)
         return attn_dense_tc5_pair(&mq, &mk, &mv, out, lse, batch, lq, lk, heads, kv_heads, scale,
-                                   status, stream);
+                                   status, stream, peer);
     dim3 grid((lq + BM - 1) / BM, heads, batch);
     return launch<128, false>(mq, mk, mv, p, grid, stream);
 }

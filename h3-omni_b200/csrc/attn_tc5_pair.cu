@@ -52,6 +52,9 @@ struct PairParams {
     __nv_bfloat16 *out;
     float *lse;
     int *status;
+    // sequence-gather fused into the epilogue (see PeerOutput); rows_per_rank == 0: off
+    __nv_bfloat16 *peer_out[16];
+    unsigned rows_per_rank, rank, total_heads;
 };
 
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
@@ -378,7 +381,15 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const float inv = 1.0f / l;
             const int row = q_row0 + t * PBM + r;
             const bool store = row < p.lq;
-            __nv_bfloat16 *dst = p.out + (((size_t)batch * p.lq + row) * p.heads + head) * PHD;
+            __nv_bfloat16 *dst;
+            if (p.rows_per_rank) {
+                // this row belongs to another rank's row shard: store it there, in place
+                const unsigned owner = (unsigned)row / p.rows_per_rank, local = (unsigned)row % p.rows_per_rank;
+                dst = p.peer_out[store ? owner : 0] +
+                      ((size_t)local * p.total_heads + (size_t)p.rank * p.heads + head) * PHD;
+            } else {
+                dst = p.out + (((size_t)batch * p.lq + row) * p.heads + head) * PHD;
+            }
             if (store && p.lse)
                 p.lse[((size_t)batch * p.heads + head) * p.lq + row] = m_ref * p.scale + __logf(l);
 #pragma unroll
@@ -421,7 +432,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 cudaError_t attn_dense_tc5_pair(const CUtensorMap_st *mq, const CUtensorMap_st *mk,
                                 const CUtensorMap_st *mv, void *out, float *lse, unsigned batch,
                                 unsigned lq, unsigned lk, unsigned heads, unsigned kv_heads,
-                                float scale, int *status, cudaStream_t stream) {
+                                float scale, int *status, cudaStream_t stream, const PeerOutput *peer) {
     static thread_local int configured_device = -1;
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
@@ -442,6 +453,13 @@ cudaError_t attn_dense_tc5_pair(const CUtensorMap_st *mq, const CUtensorMap_st *
     p.out = static_cast<__nv_bfloat16 *>(out);
     p.lse = lse;
     p.status = status;
+    if (peer) {
+        if (batch != 1 || !peer->rows_per_rank) return cudaErrorInvalidValue;
+        for (int i = 0; i < 16; i++) p.peer_out[i] = static_cast<__nv_bfloat16 *>(peer->base[i]);
+        p.rows_per_rank = peer->rows_per_rank;
+        p.rank = peer->rank;
+        p.total_heads = peer->total_heads;
+    }
     dim3 grid((lq + 2 * PBM - 1) / (2 * PBM), heads, batch);
     attn_tc5_pair_kernel<<<grid, PAIR_THREADS, PAIR_SMEM_BYTES, stream>>>(*mq, *mk, *mv, p);
     return cudaGetLastError();

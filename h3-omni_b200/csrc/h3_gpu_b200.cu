@@ -911,3 +911,41 @@ extern "C" int h3b_exchange_gather_heads_bf16(h3b_exchange *x, int slot, const h
                                               uint32_t rows, uint32_t heads, uint32_t dim) {
     return exchange_run(x, true, slot, src, rows, heads, dim);
 }
+
+// Attention with the sequence-gather fused into its epilogue: every rank attends all
+// `sequence` rows for its heads / ranks heads (q, k, v: [>= sequence][heads/ranks][128], e.g.
+// the scatter slots) and each finished output row is stored straight into the row shard of the
+// rank that owns it, slot `slot` of that rank's window laid out [rows][heads][128]. One
+// attention launch plus a one-warp epoch handshake replace attention + gather kernel.
+extern "C" int h3b_exchange_sdpa_gather_bf16(h3b_exchange *x, int slot, const h3_gpu_tensor *q,
+                                             const h3_gpu_tensor *k, const h3_gpu_tensor *v,
+                                             uint32_t sequence, uint32_t rows, uint32_t heads,
+                                             float scale) {
+    if (!x) return 0;
+    h3_gpu *g = x->gpu;
+    if (!x->connected || slot < 0 || slot >= x->slots || !heads || heads % x->ranks || !rows ||
+        (size_t)rows * heads * 128 > x->slot_elements || (size_t)sequence > (size_t)rows * x->ranks) {
+        set_error(g, "fused attention+gather: not connected, bad slot or shape (%u rows x %d ranks, %u heads)",
+                  rows, x->ranks, heads);
+        return 0;
+    }
+    const uint32_t local_heads = heads / x->ranks;
+    const size_t need = (size_t)sequence * local_heads * 128;
+    if (!require_bf16(g, q, need, "attention query") || !require_bf16(g, k, need, "attention key") ||
+        !require_bf16(g, v, need, "attention value"))
+        return 0;
+    h3b::PeerOutput peer{};
+    unsigned long long *flags[16];
+    for (int p = 0; p < x->ranks; p++) {
+        peer.base[p] = x->mapped[p] + x->slot_bytes * slot;
+        flags[p] = reinterpret_cast<unsigned long long *>(x->mapped[p] + x->flags_offset);
+    }
+    peer.rows_per_rank = rows;
+    peer.rank = (unsigned)x->rank;
+    peer.total_heads = heads;
+    int *status = nullptr;
+    if (!cuda_ok(g, h3b::device_status_word(&status))) return 0;
+    return cuda_ok(g, h3b::attn_dense_tc5(nullptr, q->data, k->data, v->data, nullptr, 1, sequence, sequence,
+                                          local_heads, local_heads, scale, g->stream, &peer)) &&
+           cuda_ok(g, h3b::exchange_handshake(flags, ++x->epoch, status, x->rank, x->ranks, g->stream));
+}

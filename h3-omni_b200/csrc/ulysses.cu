@@ -70,6 +70,21 @@ __device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned l
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
+// Publish this rank's epoch in peer `peer`'s flag array, then wait (bounded, about 2 s) until
+// that peer's epoch has arrived here: its data is then complete in our window.
+__device__ __forceinline__ void epoch_handshake(unsigned long long *const *flags, unsigned long long epoch,
+                                                int *status, int rank, int peer) {
+    st_release_sys(flags[peer] + rank, epoch);
+    const unsigned long long *mine = flags[rank] + peer;
+    const unsigned long long start = clock64();
+    for (unsigned spin = 0;; spin++) {
+        if (ld_acquire_sys(mine) >= epoch) return;
+        if ((spin & 1023u) == 1023u && clock64() - start > 4000000000ull) break;
+        __nanosleep(100);
+    }
+    atomicCAS(status, 0, 1);   // timed out; the host sees status 1
+}
+
 template <bool GATHER>
 __global__ void __launch_bounds__(256)
 exchange_push_kernel(const uint4 *__restrict__ src, PushArgs a) {
@@ -108,23 +123,14 @@ exchange_push_kernel(const uint4 *__restrict__ src, PushArgs a) {
     __syncthreads();
     if (!last) return;
     if (threadIdx.x == 0) *a.done_counter = 0;   // ready for the next exchange on this stream
-    if ((int)threadIdx.x < a.ranks) {
-        const int peer = threadIdx.x;
-        st_release_sys(a.flags[peer] + a.rank, a.epoch);
-        // wait for peer's data to be in our window: its flag entry here reaches the epoch
-        const unsigned long long *mine = a.flags[a.rank] + peer;
-        const unsigned long long start = clock64();
-        bool ok = false;
-        for (unsigned spin = 0;; spin++) {
-            if (ld_acquire_sys(mine) >= a.epoch) {
-                ok = true;
-                break;
-            }
-            if ((spin & 1023u) == 1023u && clock64() - start > 4000000000ull) break;   // ~2 s
-            __nanosleep(100);
-        }
-        if (!ok) atomicCAS(a.status, 0, 1);   // wait timed out; the host sees status 1
-    }
+    if ((int)threadIdx.x < a.ranks) epoch_handshake(a.flags, a.epoch, a.status, a.rank, threadIdx.x);
+}
+
+// One launch of `ranks` threads after a kernel that already stored into the peers' windows
+// (stream order makes that kernel's stores precede the release below).
+__global__ void exchange_handshake_kernel(PushArgs a) {
+    __threadfence_system();
+    if ((int)threadIdx.x < a.ranks) epoch_handshake(a.flags, a.epoch, a.status, a.rank, threadIdx.x);
 }
 
 }  // namespace
@@ -159,6 +165,19 @@ cudaError_t exchange_push(bool gather, const void *src, void *const window[], un
         exchange_push_kernel<true><<<blocks, 256, 0, stream>>>(static_cast<const uint4 *>(src), a);
     else
         exchange_push_kernel<false><<<blocks, 256, 0, stream>>>(static_cast<const uint4 *>(src), a);
+    return cudaGetLastError();
+}
+
+cudaError_t exchange_handshake(unsigned long long *const flags[], unsigned long long epoch, int *status,
+                               int rank, int ranks, cudaStream_t stream) {
+    if (ranks < 1 || ranks > MAX_RANKS) return cudaErrorInvalidValue;
+    PushArgs a{};
+    for (int p = 0; p < ranks; p++) a.flags[p] = flags[p];
+    a.epoch = epoch;
+    a.status = status;
+    a.rank = rank;
+    a.ranks = ranks;
+    exchange_handshake_kernel<<<1, 32, 0, stream>>>(a);
     return cudaGetLastError();
 }
 

@@ -210,6 +210,15 @@ int h3b_exchange_scatter_heads_bf16(h3b_exchange *exchange, int slot, const h3_g
 int h3b_exchange_gather_heads_bf16(h3b_exchange *exchange, int slot, const h3_gpu_tensor *src,
                                    uint32_t rows, uint32_t heads, uint32_t dim);
 
+/* Attention over this rank's heads/ranks heads with the sequence-gather fused into the kernel's
+ * epilogue: q, k, v are [>= sequence][heads/ranks][128] (typically the scatter slots); each output
+ * row is stored by the attention kernel itself into the row shard of the rank that owns the row -
+ * slot `slot` of that rank's window, [rows][heads][128] - followed by the epoch handshake.
+ * Rows >= sequence of the last shard are left untouched. */
+int h3b_exchange_sdpa_gather_bf16(h3b_exchange *exchange, int slot, const h3_gpu_tensor *q,
+                                  const h3_gpu_tensor *k, const h3_gpu_tensor *v, uint32_t sequence,
+                                  uint32_t rows, uint32_t heads, float scale);
+
 /* VSA introspection for tests and tools: geometry, an override for the number of kept
  * video tiles (the reference fixes ceil(10 %)), and device pointers of the work buffers
  * of the last h3_gpu_vsa_bf16 call. which: 0 map, 1 sizes, 2-4 tiled q/k/v, 5 sparse out,

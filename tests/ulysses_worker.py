@@ -108,6 +108,11 @@ def main():
         assert lib.h3b_exchange_gather_heads_bf16(x, 3, out2, rows, H, D), gpu.error()
         fused = gpu.read(slots[3], (rows, H, D))
         assert np.array_equal(fused[:n], gathered[:n]), "fused gather differs from the NCCL gather"
+        # attention with the gather fused into its epilogue: same bits, one launch less
+        gpu.call("zero", slots[3])
+        assert lib.h3b_exchange_sdpa_gather_bf16(x, 3, slots[0], slots[1], slots[2], L, rows, H, scale), gpu.error()
+        fused2 = gpu.read(slots[3], (rows, H, D))
+        assert np.array_equal(fused2[:n], gathered[:n]), "attention with fused gather differs"
         assert gpu.device_status() == 0
     for t in slots:
         lib.h3_gpu_tensor_free(t)
