@@ -456,8 +456,8 @@ def dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_o
                 for i, t in enumerate((tq, tk, tv)):
                     if not lib.h3b_exchange_scatter_heads_bf16(exchange, i, t, rows, HEADS, DIM):
                         raise RuntimeError(gpu.error())
-                gpu.call("sdpa_bf16", tscr, slots[0], slots[1], slots[2], plan.sequence, local_heads, DIM, SCALE)
-                if not lib.h3b_exchange_gather_heads_bf16(exchange, 3, tscr, rows, HEADS, DIM):
+                if not lib.h3b_exchange_sdpa_gather_bf16(exchange, 3, slots[0], slots[1], slots[2], plan.sequence,
+                                                         rows, HEADS, SCALE):
                     raise RuntimeError(gpu.error())
                 gpu.call("copy_bf16", to, 0, slots[3], 0, rows * HEADS * DIM)   # window -> torch tensor
             else:
