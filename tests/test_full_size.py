@@ -1,0 +1,133 @@
+"""Parity at the benchmark's full sizes, through checks that do not need a full CPU recomputation.
+
+C2 (dense joint attention, L=52,352, H=24), C5 (live: 12,960 queries against 64,800 keys) and
+C3 (video sparse attention, 905 tiles, keep 12.5 %): sampled query rows against the FP64
+recomputation of the reference's attention microbenchmark (65 rows x all heads,
+tests/serving/profile/attn_bench.cu:23-55,105-130), head-split bit-exactness
+(tests/live/sharding.py:38-46), linearity in V, and for the sparse path the defining properties
+of the index lists plus sampled query tiles recomputed from the selected keys.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from conftest import metrics
+
+pytestmark = pytest.mark.gpu
+SCALE = float(1.0 / np.sqrt(128.0))
+
+
+def sampled_rows(L, count=65, seed=0):
+    rng = np.random.default_rng(seed)
+    rows = np.unique(np.concatenate([[0, 127, 128, 255, 256, L - 1], rng.integers(0, L, count)]))
+    return rows[:count].astype(np.int32)
+
+
+def test_c2_dense_full_size(gpu, oracle):
+    L, H = 51840 + 512, 24
+    q, k, v = (oracle.normal_bf16((L, H, 128), 1002 + i) for i in range(3))
+    tq, tk, tv = gpu.tensor(q), gpu.tensor(k), gpu.tensor(v)
+    ty = gpu.empty_bf16(q.size)
+    gpu.call("sdpa_bf16", ty, tq, tk, tv, L, H, 128, SCALE)
+    out = gpu.read(ty, q.shape)
+    assert gpu.device_status() == 0
+    rows = sampled_rows(L)
+    want = oracle.attention_rows_f64(rows, q, k, v, SCALE)
+    got = oracle.from_bf16(out[rows])
+    m = metrics(got, want)
+    assert np.isfinite(oracle.from_bf16(out)).all()
+    assert m["max_abs"] <= 1e-2 and m["cosine"] >= 0.9999 and m["rel_l2"] <= 0.008, m
+    # head split: 24 heads at once == heads 0-11 and 12-23 separately, bit for bit
+    for lo in (0, 12):
+        th = gpu.empty_bf16(L * 12 * 128)
+        parts = [gpu.tensor(np.ascontiguousarray(x[:, lo:lo + 12])) for x in (q, k, v)]
+        gpu.call("sdpa_bf16", th, *parts, L, 12, 128, SCALE)
+        assert np.array_equal(gpu.read(th, (L, 12, 128)), out[:, lo:lo + 12])
+        for t in [th] + parts:
+            gpu.free(t)
+    # linearity in V on the sampled rows: attention(q, k, -v) == -attention(q, k, v) exactly
+    # (bf16 negation is exact and every product changes sign), a whole-pipeline sanity check
+    neg = gpu.tensor(v ^ np.uint16(0x8000))
+    gpu.call("sdpa_bf16", ty, tq, tk, neg, L, H, 128, SCALE)
+    assert np.array_equal(gpu.read(ty, q.shape)[rows], out[rows] ^ np.uint16(0x8000))
+    for t in (tq, tk, tv, ty, neg):
+        gpu.free(t)
+
+
+def test_c5_live_full_size(gpu, oracle):
+    """Last step of the live workload: 12,960 query rows against 64,800 key rows, row offsets."""
+    nq, nk, H = 12960, 64800, 24
+    q = oracle.normal_bf16((nq + 100, H, 128), 1005)
+    k = oracle.normal_bf16((nk + 50, H, 128), 1006)
+    v = oracle.normal_bf16((nk + 50, H, 128), 1007)
+    ty = gpu.tensor(np.zeros((nq, H, 128), dtype=np.uint16))
+    tq, tk, tv = gpu.tensor(q), gpu.tensor(k), gpu.tensor(v)
+    gpu.call("cross_attention_bf16", ty, 0, tq, 100, tk, tv, 50, nq, nk, H)
+    out = gpu.read(ty, (nq, H, 128))
+    rows = sampled_rows(nq, 40, 5)
+    want = oracle.attention_rows_f64(rows, q[100:], k[50:], v[50:], SCALE)
+    m = metrics(oracle.from_bf16(out[rows]), want)
+    assert m["max_abs"] <= 1e-2 and m["cosine"] >= 0.9999 and m["rel_l2"] <= 0.004, m
+    assert gpu.device_status() == 0
+    for t in (tq, tk, tv, ty):
+        gpu.free(t)
+
+
+def test_c3_vsa_full_size(gpu, oracle):
+    text, audio, grid, heads = 64, 512, (32, 30, 54), 24
+    vmap = oracle.VsaMap(text, audio, *grid)
+    T, P = vmap.tiles, vmap.prefix
+    assert (T, P) == (905, 9)
+    keep = (T - P) // 8
+    vsa = gpu.call("vsa_new", text, audio, *grid, heads)
+    assert gpu.lib.h3b_vsa_set_keep(vsa, keep) and gpu.lib.h3b_vsa_trace_scores(vsa, 1)
+    q, k, v = (oracle.normal_bf16((vmap.rows, heads, 128), 1003 + i) for i in range(3))
+    gate = oracle.normal_bf16((vmap.rows, heads, 128), 1013, 0.3)
+    out = gpu.tensor(np.zeros(q.shape, dtype=np.uint16))
+    tensors = [gpu.tensor(x) for x in (q, k, v, gate)]
+    assert gpu.lib.h3_gpu_vsa_bf16(vsa, out, *tensors), gpu.error()
+    got = gpu.read(out, q.shape)
+    buf = lambda which, shape, dtype: gpu.read_device(gpu.lib.h3b_vsa_buffer(vsa, which), shape, dtype)
+    counts = buf(10, (heads, T), np.int32)
+    indices = buf(9, (heads, T, T), np.int32)
+    scores = buf(12, (heads, T, T), np.float32)
+    sparse = buf(5, (heads, T * 64, 128), np.uint16)
+    compression = buf(11, (heads, T, 128), np.float32)
+    tiled = [buf(2 + i, (heads, T * 64, 128), np.uint16) for i in range(3)]
+    gpu.lib.h3_gpu_vsa_free(vsa)
+    assert gpu.device_status() == 0
+    # index lists: sizes, order, prefix always kept, and the top-k property itself
+    assert (counts[:, :P] == T).all() and (counts[:, P:] == P + keep).all()
+    rng = np.random.default_rng(3)
+    for h, qt in zip(rng.integers(0, heads, 200), rng.integers(P, T, 200)):
+        chosen = indices[h, qt, :counts[h, qt]]
+        assert (np.diff(chosen) > 0).all() and list(chosen[:P]) == list(range(P))
+        video = chosen[P:]
+        rest = np.setdiff1d(np.arange(P, T), video)
+        assert scores[h, qt, video].min() >= scores[h, qt, rest].max()
+    # pooled scores against the oracle on a few heads (bit-exact), lists follow from them
+    for h in (0, 11, 23):
+        _, pq = oracle.vsa_tile_pool(np.ascontiguousarray(q[:, h:h + 1]), vmap, want_tiled=False)
+        _, pk = oracle.vsa_tile_pool(np.ascontiguousarray(k[:, h:h + 1]), vmap, want_tiled=False)
+        want_scores = oracle.vsa_scores(pq, pk, np.float32(SCALE))
+        assert np.array_equal(want_scores[0].view(np.uint32), scores[h].view(np.uint32))
+        want_idx, want_cnt = oracle.vsa_select(want_scores, P, keep)
+        assert np.array_equal(want_cnt[0], counts[h])
+        valid = np.arange(T)[None, :] < want_cnt[0][:, None]
+        assert np.array_equal(want_idx[0][valid], indices[h][valid])
+    # fine stage: sampled (head, query tile) pairs recomputed from exactly the selected keys
+    worst = 0.0
+    for h, qt in zip(rng.integers(0, heads, 12), rng.integers(0, T, 12)):
+        chosen = indices[h, qt, :counts[h, qt]]
+        keys = np.concatenate([np.arange(t * 64, t * 64 + vmap.sizes[t]) for t in chosen])
+        qs = tiled[0][h, qt * 64:qt * 64 + vmap.sizes[qt]][None, :, None, :]
+        ks = tiled[1][h, keys][None, :, None, :]
+        vs = tiled[2][h, keys][None, :, None, :]
+        want, _ = oracle.attention(qs, ks, vs, SCALE)
+        have = oracle.from_bf16(sparse[h, qt * 64:qt * 64 + vmap.sizes[qt]])
+        worst = max(worst, float(np.abs(have - want[0, :, 0]).max()))
+    assert worst <= 1e-2, worst
+    # merge: out == bf16(fma(bf16(compression), gate, sparse)) on every token row (exact)
+    want_out = oracle.vsa_untile_merge(sparse, gate, compression, vmap)
+    assert np.array_equal(want_out, got)
