@@ -582,8 +582,32 @@ def live_part(gpu, torch, device, out, events, wrap, g):
         nk = nq + min(s, 4) * nq
         ms = events(lambda: gpu.call("cross_attention_bf16", to, 0, tq, 0, tk, tv, 0, nq, nk, HEADS), 3, 1)
         steps.append({"step": s, "key_rows": nk, "ms": ms, "tflops": 4.0 * nq * nk * HEADS * DIM / ms / 1e9})
+    # steady state (4 history chunks + the current one): the reference's way - concatenate the
+    # five K and V ranges with device copies, then attend - against the segmented call
+    kc, vc = torch.empty_like(k), torch.empty_like(v)
+    tkc, tvc = wrap(kc), wrap(vc)
+    n = nq * HEADS * DIM
+
+    def concat_then_attend():
+        for i in range(5):
+            gpu.call("copy_bf16", tkc, i * n, tk, i * n, n)
+            gpu.call("copy_bf16", tvc, i * n, tv, i * n, n)
+        gpu.call("cross_attention_bf16", to, 0, tq, 0, tkc, tvc, 0, nq, 5 * nq, HEADS)
+
+    keys = (C.c_void_p * 5)(*[tk] * 5)
+    values = (C.c_void_p * 5)(*[tv] * 5)
+    offsets = (C.c_size_t * 5)(*[i * nq for i in range(5)])
+    counts = (C.c_uint32 * 5)(*[nq] * 5)
+
+    def segmented():
+        if not gpu.lib.h3b_cross_attention_segments_bf16(gpu.gpu, to, 0, tq, 0, nq, HEADS, 5, keys, values,
+                                                         offsets, counts):
+            raise RuntimeError(gpu.error())
+
     out["live"] = {"workload": "query chunk 12960 rows, keys 12960 + min(step,4)*12960 history rows, H=%d" % HEADS,
-                   "steps": steps, "total_ms": sum(x["ms"] for x in steps)}
+                   "steps": steps, "total_ms": sum(x["ms"] for x in steps),
+                   "steady_state_concat_copies_then_attention_ms": events(concat_then_attend, 3, 1),
+                   "steady_state_segmented_call_ms": events(segmented, 3, 1)}
 
 
 if __name__ == "__main__":

@@ -29,7 +29,13 @@ cudaError_t attn_dense_tc5_pair(const ::CUtensorMap_st *mq, const ::CUtensorMap_
                                 const ::CUtensorMap_st *mv, void *out, float *lse, unsigned batch,
                                 unsigned lq, unsigned lk, unsigned heads, unsigned kv_heads,
                                 float scale, int *status, cudaStream_t stream,
-                                const PeerOutput *peer = nullptr);
+                                const PeerOutput *peer = nullptr, unsigned segments = 0,
+                                const unsigned *segment_rows = nullptr);
+// Rectangular attention of lq query rows against the concatenation of `segments` (<= 6) K/V row
+// ranges, each token-major [rows_s][heads][128], without concatenating them (batch 1).
+cudaError_t attn_segments_tc5(void *out, const void *q, const void *const *k, const void *const *v,
+                              const unsigned *segment_rows, unsigned segments, unsigned lq,
+                              unsigned heads, float scale, cudaStream_t stream);
 // Head-major tiled [H][tiles*64][128] bf16 with per-(head, query tile) KV tile lists.
 cudaError_t attn_sparse_tc5(void *out, const void *q, const void *k, const void *v, float *lse,
                             const int *indices, const int *counts, const int *sizes,

@@ -492,6 +492,33 @@ cudaError_t attn_dense_tc5(void *out, const void *q, const void *k, const void *
     return launch<128, false>(mq, mk, mv, p, grid, stream);
 }
 
+cudaError_t attn_segments_tc5(void *out, const void *q, const void *const *k, const void *const *v,
+                              const unsigned *segment_rows, unsigned segments, unsigned lq,
+                              unsigned heads, float scale, cudaStream_t stream) {
+    if (!segments || segments > 6u || !lq || !heads || heads > 65535u) return cudaErrorInvalidValue;
+    int *status = nullptr;
+    cudaError_t e = device_status_word(&status);
+    if (e != cudaSuccess) return e;
+    CUtensorMap mq, mk[6], mv[6];
+    const uint32_t box[4] = {64, 1, 128, 1};
+    unsigned total = 0;
+    {
+        const uint64_t dims[4] = {128, heads, lq, 1};
+        const uint64_t strides[3] = {256, (uint64_t)heads * 256, (uint64_t)lq * heads * 256};
+        if ((e = make_map(&mq, q, dims, strides, box)) != cudaSuccess) return e;
+    }
+    for (unsigned s = 0; s < segments; s++) {
+        if (!segment_rows[s] || !k[s] || !v[s]) return cudaErrorInvalidValue;
+        const uint64_t dims[4] = {128, heads, segment_rows[s], 1};
+        const uint64_t strides[3] = {256, (uint64_t)heads * 256, (uint64_t)segment_rows[s] * heads * 256};
+        if ((e = make_map(&mk[s], k[s], dims, strides, box)) != cudaSuccess) return e;
+        if ((e = make_map(&mv[s], v[s], dims, strides, box)) != cudaSuccess) return e;
+        total += segment_rows[s];
+    }
+    return attn_dense_tc5_pair(&mq, mk, mv, out, nullptr, 1, lq, total, heads, heads, scale, status, stream,
+                               nullptr, segments, segment_rows);
+}
+
 cudaError_t attn_sparse_tc5(void *out, const void *q, const void *k, const void *v, float *lse,
                             const int *indices, const int *counts, const int *sizes,
                             unsigned tiles, unsigned heads, cudaStream_t stream) {

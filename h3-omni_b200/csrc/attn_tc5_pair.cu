@@ -46,7 +46,16 @@ __device__ long long g_pair_trace[32];
 #define TRACE_ADD(slot)
 #endif
 
+constexpr int PAIR_MAX_SEGMENTS = 6;
+// K/V may be given as up to six separate row ranges (live mode: text, sink, two recent chunks,
+// current chunk ...) that are attended as if concatenated; every range has its own tensor maps
+// and may end in a partial tile.
+struct PairKvMaps {
+    CUtensorMap k[PAIR_MAX_SEGMENTS], v[PAIR_MAX_SEGMENTS];
+};
+
 struct PairParams {
+    int segments, seg_rows[PAIR_MAX_SEGMENTS];
     int lq, lk, heads, kv_heads;
     float scale, scale_log2;
     __nv_bfloat16 *out;
@@ -58,8 +67,8 @@ struct PairParams {
 };
 
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
-attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                     const __grid_constant__ CUtensorMap map_v, const PairParams p) {
+attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ PairKvMaps kv,
+                     const PairParams p) {
     constexpr int ST = PAIR_STAGES;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[1 + 2 * ST + 6];
@@ -82,7 +91,8 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int head = blockIdx.y, batch = blockIdx.z;
     const int kv_head = head / (p.heads / p.kv_heads);
     const int q_row0 = blockIdx.x * 2 * PBM;
-    const int n_tiles = (p.lk + PBN - 1) / PBN;
+    int n_tiles = 0;   // key tiles over all segments
+    for (int s = 0; s < p.segments; s++) n_tiles += (p.seg_rows[s] + PBN - 1) / PBN;
 
     if (tid == 0) {
         mbar_init(bar_q_full, 1);
@@ -113,22 +123,30 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             tma_prefetch_desc(&map_q);
-            tma_prefetch_desc(&map_k);
-            tma_prefetch_desc(&map_v);
             mbar_arrive_expect_tx(bar_q_full, PAIR_Q_BYTES);
             for (int t = 0; t < 2; t++) {
                 const uint32_t dst = q_smem + t * (PAIR_Q_BYTES / 2);
                 tma_load_4d(dst, &map_q, bar_q_full, 0, head, q_row0 + t * PBM, batch);
                 tma_load_4d(dst + PAIR_HALF_BYTES, &map_q, bar_q_full, 64, head, q_row0 + t * PBM, batch);
             }
-            for (int idx = 0; idx < 2 * n_tiles; idx++) {   // even: K tile idx/2, odd: V tile idx/2
-                const int s = idx % ST, use = idx / ST;
-                if (use > 0 && !mbar_wait(bar_empty(s), (use - 1) & 1, &abort_word)) break;
-                const uint32_t dst = ring + s * PAIR_TILE_BYTES;
-                const void *map = (idx & 1) ? (const void *)&map_v : (const void *)&map_k;
-                mbar_arrive_expect_tx(bar_full(s), PAIR_TILE_BYTES);
-                tma_load_4d(dst, map, bar_full(s), 0, kv_head, (idx / 2) * PBN, batch);
-                tma_load_4d(dst + PAIR_HALF_BYTES, map, bar_full(s), 64, kv_head, (idx / 2) * PBN, batch);
+            int idx = 0;   // ring position: even = K tile, odd = V tile
+            bool ok = true;
+            for (int seg = 0; ok && seg < p.segments; seg++) {
+                const int tiles = (p.seg_rows[seg] + PBN - 1) / PBN;
+                for (int tile = 0; ok && tile < tiles; tile++) {
+                    for (int which = 0; which < 2; which++, idx++) {
+                        const int s = idx % ST, use = idx / ST;
+                        if (use > 0 && !mbar_wait(bar_empty(s), (use - 1) & 1, &abort_word)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t dst = ring + s * PAIR_TILE_BYTES;
+                        const void *map = which ? (const void *)&kv.v[seg] : (const void *)&kv.k[seg];
+                        mbar_arrive_expect_tx(bar_full(s), PAIR_TILE_BYTES);
+                        tma_load_4d(dst, map, bar_full(s), 0, kv_head, tile * PBN, batch);
+                        tma_load_4d(dst + PAIR_HALF_BYTES, map, bar_full(s), 64, kv_head, tile * PBN, batch);
+                    }
+                }
             }
         }
     } else if (warp == 9) {
@@ -256,8 +274,14 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         long long g_pair_trace_local[8] = {};
         const long long trace_begin = clock64();
 #endif
+        int seg = 0, seg_tile = 0;   // which segment, which tile of it, step j is
         for (int j = 0; j < n_tiles; j++) {
-            const int nvalid = min(PBN, p.lk - j * PBN);
+            while (seg_tile * PBN >= p.seg_rows[seg]) {
+                seg++;
+                seg_tile = 0;
+            }
+            const int nvalid = min(PBN, p.seg_rows[seg] - seg_tile * PBN);
+            seg_tile++;
             {
                 TRACE_T0();
                 alive = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), j & 1, &abort_word));
@@ -432,7 +456,8 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 cudaError_t attn_dense_tc5_pair(const CUtensorMap_st *mq, const CUtensorMap_st *mk,
                                 const CUtensorMap_st *mv, void *out, float *lse, unsigned batch,
                                 unsigned lq, unsigned lk, unsigned heads, unsigned kv_heads,
-                                float scale, int *status, cudaStream_t stream, const PeerOutput *peer) {
+                                float scale, int *status, cudaStream_t stream, const PeerOutput *peer,
+                                unsigned segments, const unsigned *segment_rows) {
     static thread_local int configured_device = -1;
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
@@ -443,7 +468,17 @@ cudaError_t attn_dense_tc5_pair(const CUtensorMap_st *mq, const CUtensorMap_st *
         if (e != cudaSuccess) return e;
         configured_device = device;
     }
+    // mk / mv point to `segments` maps each; without a segment list: one range of lk rows
+    if (segments > (unsigned)PAIR_MAX_SEGMENTS || (segments > 1 && batch != 1)) return cudaErrorInvalidValue;
+    PairKvMaps kv{};
     PairParams p{};
+    p.segments = segments ? (int)segments : 1;
+    for (int i = 0; i < p.segments; i++) {
+        kv.k[i] = mk[i];
+        kv.v[i] = mv[i];
+        p.seg_rows[i] = segments ? (int)segment_rows[i] : (int)lk;
+        if (p.seg_rows[i] <= 0) return cudaErrorInvalidValue;
+    }
     p.lq = (int)lq;
     p.lk = (int)lk;
     p.heads = (int)heads;
@@ -461,7 +496,7 @@ cudaError_t attn_dense_tc5_pair(const CUtensorMap_st *mq, const CUtensorMap_st *
         p.total_heads = peer->total_heads;
     }
     dim3 grid((lq + 2 * PBM - 1) / (2 * PBM), heads, batch);
-    attn_tc5_pair_kernel<<<grid, PAIR_THREADS, PAIR_SMEM_BYTES, stream>>>(*mq, *mk, *mv, p);
+    attn_tc5_pair_kernel<<<grid, PAIR_THREADS, PAIR_SMEM_BYTES, stream>>>(*mq, kv, p);
     return cudaGetLastError();
 }
 

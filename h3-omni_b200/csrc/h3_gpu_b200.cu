@@ -420,6 +420,43 @@ extern "C" int h3_gpu_cross_attention_bf16(h3_gpu *g, h3_gpu_tensor *y, size_t y
                                            nullptr, nq, nk, heads, 1.0f / sqrtf(128.0f), g->stream));
 }
 
+// Live-mode attention without the per-layer concatenation copies (an addition; the reference
+// builds text | sink | recent0 | recent1 | current by device copies first, h3_dit_live.inc:81-94):
+// query rows attend the listed K/V row ranges as if they were one tensor. Every range is
+// [>= kv_row[s] + kv_rows[s]][heads][128] bf16; at most six ranges; scale 1/sqrt(128) as in
+// h3_gpu_cross_attention_bf16.
+extern "C" int h3b_cross_attention_segments_bf16(h3_gpu *g, h3_gpu_tensor *y, size_t yo,
+                                                 const h3_gpu_tensor *q, size_t qo, uint32_t nq,
+                                                 uint32_t heads, uint32_t segments,
+                                                 const h3_gpu_tensor *const *k,
+                                                 const h3_gpu_tensor *const *v, const size_t *kv_row,
+                                                 const uint32_t *kv_rows) {
+    if (!g) return 0;
+    const size_t width = (size_t)heads * 128;
+    if (!nq || !heads || !segments || segments > 6 || !k || !v || !kv_row || !kv_rows) {
+        set_error(g, "segmented live attention: 1 to 6 key/value ranges and a non-empty query");
+        return 0;
+    }
+    if (!require_bf16(g, y, (yo + nq) * width, "live output") ||
+        !require_bf16(g, q, (qo + nq) * width, "live query"))
+        return 0;
+    const void *kp[6], *vp[6];
+    for (uint32_t s = 0; s < segments; s++) {
+        if (!kv_rows[s]) {
+            set_error(g, "segmented live attention: range %u is empty", s);
+            return 0;
+        }
+        if (!require_bf16(g, k[s], (kv_row[s] + kv_rows[s]) * width, "live key") ||
+            !require_bf16(g, v[s], (kv_row[s] + kv_rows[s]) * width, "live value"))
+            return 0;
+        kp[s] = static_cast<const uint16_t *>(k[s]->data) + kv_row[s] * width;
+        vp[s] = static_cast<const uint16_t *>(v[s]->data) + kv_row[s] * width;
+    }
+    return cuda_ok(g, h3b::attn_segments_tc5(static_cast<uint16_t *>(y->data) + yo * width,
+                                             static_cast<const uint16_t *>(q->data) + qo * width, kp, vp,
+                                             kv_rows, segments, nq, heads, 1.0f / sqrtf(128.0f), g->stream));
+}
+
 // Dense attention straight from and to host memory (an addition; the reference has no
 // host-buffer attention call). The heads are independent, so the work is cut into head groups
 // and pipelined over three streams: while group g is computed, group g+1 is copied in and

@@ -172,6 +172,18 @@ void *h3b_tensor_data(const h3_gpu_tensor *tensor);
 int h3b_gpu_set_stream(h3_gpu *gpu, cudaStream_t stream);
 cudaStream_t h3b_gpu_stream(const h3_gpu *gpu);
 
+/* Live-mode attention over K/V given as up to six separate row ranges (text, sink, recent
+ * chunks, current chunk ...) attended as if concatenated - without the concatenation copies the
+ * reference makes per layer (h3_dit_live.inc:81-94). keys[s] / values[s] are
+ * [>= kv_row[s] + kv_rows[s]][heads][128] bf16; rows kv_row[s] .. +kv_rows[s] of range s are used,
+ * in range order. Scale is 1/sqrt(128) as in h3_gpu_cross_attention_bf16. */
+int h3b_cross_attention_segments_bf16(h3_gpu *gpu, h3_gpu_tensor *out, size_t out_row,
+                                      const h3_gpu_tensor *q, size_t q_row, uint32_t query_rows,
+                                      uint32_t heads, uint32_t segments,
+                                      const h3_gpu_tensor *const *keys,
+                                      const h3_gpu_tensor *const *values, const size_t *kv_row,
+                                      const uint32_t *kv_rows);
+
 /* Dense attention from and to HOST memory, head dim 128: q, k, v, out are token-major
  * [sequence][heads][128] bf16 in host memory (pinned for full speed). The heads are cut into
  * head_groups groups (heads % head_groups == 0) and copy-in, kernel and copy-out of

@@ -243,3 +243,39 @@ def test_host_buffer_attention_matches_device_path(gpu, oracle, groups):
                                           128, SCALE, 3)
     assert "do not split into 3 groups" in gpu.error()
     assert gpu.device_status() == 0
+
+
+@pytest.mark.parametrize("nq,ranges,H", [(300, [77, 405, 1000, 128, 300], 4), (64, [5], 2),
+                                          (405, [129, 1, 127, 256, 33, 700], 7)])
+def test_segmented_live_attention_equals_concatenated(gpu, oracle, nq, ranges, H):
+    """h3b_cross_attention_segments_bf16 over separate K/V ranges == h3_gpu_cross_attention_bf16
+    over their concatenation (the reference's live path, h3_dit_live.inc:81-99). Ranges that
+    are multiples of 128 rows give the same bits; ragged ones regroup the key tiles, so those
+    are compared by tolerance and against the oracle."""
+    q = oracle.normal_bf16((nq + 9, H, 128), 500)
+    ks = [oracle.normal_bf16((r + 3, H, 128), 510 + i) for i, r in enumerate(ranges)]
+    vs = [oracle.normal_bf16((r + 3, H, 128), 520 + i) for i, r in enumerate(ranges)]
+    kcat = np.concatenate([x[3:] for x in ks])
+    vcat = np.concatenate([x[3:] for x in vs])
+    tq = gpu.tensor(q)
+    want_t = gpu.tensor(np.zeros((nq, H, 128), dtype=np.uint16))
+    gpu.call("cross_attention_bf16", want_t, 0, tq, 9, gpu.tensor(kcat), gpu.tensor(vcat), 0, nq, len(kcat), H)
+    concat = gpu.read(want_t, (nq, H, 128))
+    n = len(ranges)
+    tk = (C.c_void_p * n)(*[gpu.tensor(x) for x in ks])
+    tv = (C.c_void_p * n)(*[gpu.tensor(x) for x in vs])
+    rows = (C.c_uint32 * n)(*ranges)
+    offs = (C.c_size_t * n)(*([3] * n))
+    out = gpu.tensor(np.zeros((nq + 2, H, 128), dtype=np.uint16))
+    ok = gpu.lib.h3b_cross_attention_segments_bf16(gpu.gpu, out, 2, tq, 9, nq, H, n, tk, tv, offs, rows)
+    assert ok, gpu.error()
+    got = gpu.read(out, (nq + 2, H, 128))
+    assert not got[:2].any()
+    want, _ = oracle.attention(q[None, 9:], kcat[None], vcat[None], SCALE)
+    assert_attention_close(oracle.from_bf16(got[2:]), want[0])
+    if all(r % 128 == 0 for r in ranges) or n == 1:
+        assert np.array_equal(got[2:], concat)
+    else:
+        assert np.abs(oracle.from_bf16(got[2:]) - oracle.from_bf16(concat)).max() <= 4e-3
+    assert gpu.device_status() == 0
+    assert not gpu.lib.h3b_cross_attention_segments_bf16(gpu.gpu, out, 2, tq, 9, nq, H, 7, tk, tv, offs, rows)
