@@ -220,19 +220,25 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             constexpr uint32_t idesc_qk = mma_idesc(BM, BN, 1, 0);
             constexpr uint32_t idesc_pv = mma_idesc(BM, HD, 1, 1);
             bool alive = mbar_wait(bar_q_full(), 0, &abort_word);
+            // Descriptors once per kernel (Q) or per stage (K, V); each MMA then costs one add on
+            // the low word: +2 per 32 bytes inside a 64-column half, +HALF_BYTES/16 for the second
+            // half, +128 per 16 V rows. The issuing thread shares its scheduler with busy softmax
+            // warps, so every instruction it saves keeps the tensor pipe fed.
+            const uint64_t q_desc = smem_desc_sw128(q_smem, 16, 1024);
+            const uint64_t k_proto = smem_desc_sw128(k_smem, 16, 1024);
+            const uint64_t v_proto = smem_desc_sw128(v_smem, Cfg::HALF_BYTES, 1024);   // LBO lives in the low word
+            const uint32_t q_lo = (uint32_t)q_desc, q_hi = (uint32_t)(q_desc >> 32);
+            const uint32_t k_lo0 = (uint32_t)k_proto, k_hi = (uint32_t)(k_proto >> 32);
+            const uint32_t v_lo0 = (uint32_t)v_proto, v_hi = (uint32_t)(v_proto >> 32);
             auto issue_qk = [&](int j) -> bool {
                 const int s = j % ST, sb = j % SB;
                 if (!mbar_wait(bar_k_full(s), (j / ST) & 1, &abort_word)) return false;
-                tc5_fence_after();
-                const uint32_t kd = k_smem + s * Cfg::TILE_BYTES;
+                const uint32_t k_lo = k_lo0 + s * (Cfg::TILE_BYTES >> 4);
 #pragma unroll
-                for (int kk = 0; kk < HD / 16; kk++) {
-                    const uint64_t a =
-                        smem_desc_sw128(q_smem + (kk / 4) * (Q_BYTES / 2) + (kk % 4) * 32, 16, 1024);
-                    const uint64_t b =
-                        smem_desc_sw128(kd + (kk / 4) * Cfg::HALF_BYTES + (kk % 4) * 32, 16, 1024);
-                    mma_ss(tmem + sb * BN, a, b, idesc_qk, kk > 0);
-                }
+                for (int kk = 0; kk < HD / 16; kk++)
+                    mma_ss_words(tmem + sb * BN, q_lo + (kk / 4) * (Q_BYTES / 2 >> 4) + (kk % 4) * 2, q_hi,
+                                 k_lo + (kk / 4) * (Cfg::HALF_BYTES >> 4) + (kk % 4) * 2, k_hi, idesc_qk,
+                                 kk > 0);
                 mma_commit(bar_s_full(sb));
                 mma_commit(bar_k_empty(s));
                 return true;
@@ -241,17 +247,19 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             for (int j = 0; alive && j < n_tiles; j++) {
                 if (SB == 2 && j + 1 < n_tiles && !issue_qk(j + 1)) break;
                 const int s = j % ST, sb = j % SB;
-                if (!mbar_wait(bar_p_full(sb), (j / SB) & 1, &abort_word)) break;
+                // V was requested long ago: probe it before P so the (normally immediate) wait
+                // is off the path between P arriving and the PV issue
                 if (!mbar_wait(bar_v_full(s), (j / ST) & 1, &abort_word)) break;
+                if (!mbar_wait(bar_p_full(sb), (j / SB) & 1, &abort_word)) break;
                 tc5_fence_after();
-                const uint32_t vd = v_smem + s * Cfg::TILE_BYTES;
+                // V tile [BN rows][128] is MN-major for this product: the two 64-column halves
+                // are HALF_BYTES apart, 8-row groups 1024 bytes apart.
+                const uint32_t v_lo = v_lo0 + s * (Cfg::TILE_BYTES >> 4);
+                mma_ts_words(tmem + O_COL, tmem + sb * BN, v_lo, v_hi, idesc_pv, j > 0);
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; kk++) {
-                    // V tile [BN rows][128] is MN-major for this product: the two 64-column
-                    // halves are HALF_BYTES apart, 8-row groups 1024 bytes apart.
-                    const uint64_t b = smem_desc_sw128(vd + kk * 2048, Cfg::HALF_BYTES, 1024);
-                    mma_ts(tmem + O_COL, tmem + sb * BN + kk * 8, b, idesc_pv, (j > 0) || (kk > 0));
-                }
+                for (int kk = 1; kk < BN / 16; kk++)
+                    mma_ts_words(tmem + O_COL, tmem + sb * BN + kk * 8, v_lo + kk * (2048 >> 4), v_hi,
+                                 idesc_pv, 1);
                 mma_commit(bar_v_empty(s));
                 mma_commit(bar_pv_done);
                 if (SB == 1 && j + 1 < n_tiles && !issue_qk(j + 1)) break;
