@@ -60,6 +60,24 @@ cudaError_t vsa_untile_merge(void *output, const void *tiled, const void *gate,
                              const float *compression, const int *map, int tiles, int heads,
                              cudaStream_t stream);
 
+// Q/K RMS-norm + rotary embedding of the fused QKV projection output (qkv_rope.cu), head dim 128.
+// qkv: [rows][3][heads][128] or, grouped, [rows][heads][3][128]; weights [128]; angles
+// [rows][rope_half]; all bf16.
+struct QkvRopeInput {
+    const void *qkv, *q_weight, *k_weight, *rope_cos, *rope_sin;
+    unsigned rows, heads, rope_half;
+    bool grouped;
+    float epsilon;
+};
+// q, k, v token-major [rows][heads][128].
+cudaError_t qkv_rope_token_major(const QkvRopeInput &in, void *q, void *k, void *v, cudaStream_t stream);
+// Straight into every rank's head shard [ranks*rows][heads/ranks][128] (window_x[p]: rank p's).
+cudaError_t qkv_rope_head_shards(const QkvRopeInput &in, void *const window_q[], void *const window_k[],
+                                 void *const window_v[], int rank, int ranks, cudaStream_t stream);
+// Straight into VSA tile order [heads][tiles*64][128] plus FP32 tile means [heads][tiles][128].
+cudaError_t qkv_rope_vsa_tiles(const QkvRopeInput &in, const int *map, const int *sizes, int tiles,
+                               void *const tiled[3], float *const pooled[3], cudaStream_t stream);
+
 // Ulysses local transposes (ulysses.cu): out[b][a][c] = in[a][b][c], c in 16-byte units.
 cudaError_t swap_leading_16b(void *out, const void *in, unsigned a, unsigned b, size_t c_units,
                              cudaStream_t stream);

@@ -536,6 +536,50 @@ extern "C" int h3b_sdpa_bf16_host(h3_gpu *g, uint16_t *out, const uint16_t *q, c
     return cuda_ok(g, cudaStreamSynchronize(p.d2h)) && cuda_ok(g, cudaStreamSynchronize(g->stream));
 }
 
+// ======================= Q/K norm + rotary embedding (attention's producer) =======================
+
+static int rope_input(h3_gpu *g, h3b::QkvRopeInput &in, const h3_gpu_tensor *qkv, const h3_gpu_tensor *qn,
+                      const h3_gpu_tensor *kn, const h3_gpu_tensor *co, const h3_gpu_tensor *si,
+                      uint32_t rows, uint32_t heads, uint32_t dim, uint32_t half, float eps, int grouped) {
+    if (dim != 128 || half % 4 || half * 2 > dim || !rows || !heads) {
+        set_error(g, "qkv_rope: head_dim %u / rope_half %u not supported (128; multiple of 4, <= 64)", dim, half);
+        return 0;
+    }
+    const size_t inner = (size_t)heads * dim;
+    if (!require_bf16(g, qkv, (size_t)rows * inner * 3, "QKV projection") ||
+        !require_bf16(g, qn, dim, "query norm weight") || !require_bf16(g, kn, dim, "key norm weight") ||
+        !require_bf16(g, co, (size_t)rows * half, "RoPE cosine") ||
+        !require_bf16(g, si, (size_t)rows * half, "RoPE sine"))
+        return 0;
+    in = h3b::QkvRopeInput{qkv->data, qn->data, kn->data, co->data, si->data, rows, heads, half, grouped != 0, eps};
+    return 1;
+}
+static int qkv_rope(h3_gpu *g, h3_gpu_tensor *q, h3_gpu_tensor *k, h3_gpu_tensor *v, const h3_gpu_tensor *x,
+                    const h3_gpu_tensor *qn, const h3_gpu_tensor *kn, const h3_gpu_tensor *co,
+                    const h3_gpu_tensor *si, uint32_t rows, uint32_t heads, uint32_t dim, uint32_t half,
+                    float eps, int grouped) {
+    if (!g) return 0;
+    h3b::QkvRopeInput in{};
+    if (!rope_input(g, in, x, qn, kn, co, si, rows, heads, dim, half, eps, grouped)) return 0;
+    const size_t n = (size_t)rows * heads * dim;
+    if (!require_bf16(g, q, n, "query") || !require_bf16(g, k, n, "key") || !require_bf16(g, v, n, "value"))
+        return 0;
+    return cuda_ok(g, h3b::qkv_rope_token_major(in, q->data, k->data, v->data, g->stream));
+}
+extern "C" int h3_gpu_qkv_rope_bf16(h3_gpu *g, h3_gpu_tensor *q, h3_gpu_tensor *k, h3_gpu_tensor *v,
+                                    const h3_gpu_tensor *x, const h3_gpu_tensor *qn, const h3_gpu_tensor *kn,
+                                    const h3_gpu_tensor *co, const h3_gpu_tensor *si, uint32_t s, uint32_t h,
+                                    uint32_t d, uint32_t rh, float eps) {
+    return qkv_rope(g, q, k, v, x, qn, kn, co, si, s, h, d, rh, eps, 0);
+}
+extern "C" int h3_gpu_grouped_qkv_rope_bf16(h3_gpu *g, h3_gpu_tensor *q, h3_gpu_tensor *k, h3_gpu_tensor *v,
+                                            const h3_gpu_tensor *x, const h3_gpu_tensor *qn,
+                                            const h3_gpu_tensor *kn, const h3_gpu_tensor *co,
+                                            const h3_gpu_tensor *si, uint32_t s, uint32_t h, uint32_t d,
+                                            uint32_t rh, float eps) {
+    return qkv_rope(g, q, k, v, x, qn, kn, co, si, s, h, d, rh, eps, 1);
+}
+
 // ======================= video sparse attention =======================
 
 struct h3_gpu_vsa {
@@ -660,6 +704,30 @@ extern "C" void *h3b_vsa_buffer(const h3_gpu_vsa *s, int which) {
     return all[which]->data;
 }
 
+// Everything after the tiled copies and tile means exist: scores + selection + compression,
+// the block-sparse kernel, merge back to token order (cuda/vsa.cuh:281-299).
+static int vsa_after_tiling(h3_gpu_vsa *s, h3_gpu_tensor *out, const h3_gpu_tensor *gate) {
+    h3_gpu *g = s->gpu;
+    float *pooled[3] = {(float *)s->poolq->data, (float *)s->poolk->data, (float *)s->poolv->data};
+    const int *map = (const int *)s->map->data;
+    const float scale = 1.0f / sqrtf(128.0f);
+    if (!cuda_ok(g, h3b::vsa_score_select_compress(
+                        pooled[0], pooled[1], pooled[2],
+                        s->trace_scores ? (float *)s->scores->data : nullptr,
+                        (int *)s->indices->data, (int *)s->counts->data,
+                        (float *)s->compression->data, s->tiles, s->prefix, s->keep, s->heads, scale,
+                        g->stream)))
+        return 0;
+    if (!cuda_ok(g, h3_vsa_hopper(s->out->data, s->q->data, s->k->data, s->v->data, nullptr,
+                                  (int *)s->indices->data, (int *)s->counts->data,
+                                  (int *)s->sizes->data, s->tiles, s->heads, g->stream)))
+        return 0;
+    return cuda_ok(g, h3b::vsa_untile_merge(out->data, s->out->data, gate->data,
+                                            (const float *)s->compression->data, map, s->tiles,
+                                            s->heads, g->stream));
+}
+
+
 // cuda/vsa.cuh:263-300, as three launches around the block-sparse kernel.
 extern "C" int h3_gpu_vsa_bf16(h3_gpu_vsa *s, h3_gpu_tensor *out, const h3_gpu_tensor *q,
                                const h3_gpu_tensor *k, const h3_gpu_tensor *value,
@@ -677,21 +745,28 @@ extern "C" int h3_gpu_vsa_bf16(h3_gpu_vsa *s, h3_gpu_tensor *out, const h3_gpu_t
     if (!cuda_ok(g, h3b::vsa_tile_pool3(src, tiled, pooled, map, sizes, s->tiles, s->heads, 3,
                                         g->stream)))
         return 0;
-    const float scale = 1.0f / sqrtf(128.0f);
-    if (!cuda_ok(g, h3b::vsa_score_select_compress(
-                        pooled[0], pooled[1], pooled[2],
-                        s->trace_scores ? (float *)s->scores->data : nullptr,
-                        (int *)s->indices->data, (int *)s->counts->data,
-                        (float *)s->compression->data, s->tiles, s->prefix, s->keep, s->heads, scale,
-                        g->stream)))
+    return vsa_after_tiling(s, out, gate);
+}
+
+// The same pipeline fed by the QKV projection output: norm + rotation write the tiled copies and
+// the tile means themselves (csrc/qkv_rope.cu), then the shared remainder.
+extern "C" int h3b_vsa_qkv_rope_bf16(h3_gpu_vsa *s, h3_gpu_tensor *out, const h3_gpu_tensor *qkv,
+                                     const h3_gpu_tensor *qn, const h3_gpu_tensor *kn,
+                                     const h3_gpu_tensor *co, const h3_gpu_tensor *si,
+                                     const h3_gpu_tensor *gate, uint32_t rope_half, float eps, int grouped) {
+    if (!s) return 0;
+    h3_gpu *g = s->gpu;
+    const size_t elements = (size_t)s->rows * s->heads * 128;
+    if (!require_bf16(g, out, elements, "VSA output") || !require_bf16(g, gate, elements, "VSA gate")) return 0;
+    h3b::QkvRopeInput in{};
+    if (!rope_input(g, in, qkv, qn, kn, co, si, (uint32_t)s->rows, (uint32_t)s->heads, 128, rope_half, eps, grouped))
         return 0;
-    if (!cuda_ok(g, h3_vsa_hopper(s->out->data, s->q->data, s->k->data, s->v->data, nullptr,
-                                  (int *)s->indices->data, (int *)s->counts->data,
-                                  (int *)s->sizes->data, s->tiles, s->heads, g->stream)))
+    void *tiled[3] = {s->q->data, s->k->data, s->v->data};
+    float *pooled[3] = {(float *)s->poolq->data, (float *)s->poolk->data, (float *)s->poolv->data};
+    if (!cuda_ok(g, h3b::qkv_rope_vsa_tiles(in, (const int *)s->map->data, (const int *)s->sizes->data,
+                                            s->tiles, tiled, pooled, g->stream)))
         return 0;
-    return cuda_ok(g, h3b::vsa_untile_merge(out->data, s->out->data, gate->data,
-                                            (const float *)s->compression->data, map, s->tiles,
-                                            s->heads, g->stream));
+    return vsa_after_tiling(s, out, gate);
 }
 
 // ======================= multi-GPU: communicators and Ulysses =======================
@@ -984,5 +1059,39 @@ extern "C" int h3b_exchange_sdpa_gather_bf16(h3b_exchange *x, int slot, const h3
     if (!cuda_ok(g, h3b::device_status_word(&status))) return 0;
     return cuda_ok(g, h3b::attn_dense_tc5(nullptr, q->data, k->data, v->data, nullptr, 1, sequence, sequence,
                                           local_heads, local_heads, scale, g->stream, &peer)) &&
+           cuda_ok(g, h3b::exchange_handshake(flags, ++x->epoch, status, x->rank, x->ranks, g->stream));
+}
+
+// Producer fused with the head scatter: norm + rotation store each (row, head) vector of q, k
+// and v into the owning rank's slots, then one epoch handshake for all three tensors.
+extern "C" int h3b_exchange_qkv_rope_scatter_bf16(h3b_exchange *x, int slot_q, int slot_k, int slot_v,
+                                                  const h3_gpu_tensor *qkv, const h3_gpu_tensor *qn,
+                                                  const h3_gpu_tensor *kn, const h3_gpu_tensor *co,
+                                                  const h3_gpu_tensor *si, uint32_t rows, uint32_t heads,
+                                                  uint32_t rope_half, float eps, int grouped) {
+    if (!x) return 0;
+    h3_gpu *g = x->gpu;
+    const int slots[3] = {slot_q, slot_k, slot_v};
+    bool bad = !x->connected || !heads || heads % x->ranks || (size_t)rows * heads * 128 > x->slot_elements;
+    for (int t = 0; t < 3; t++) {
+        bad = bad || slots[t] < 0 || slots[t] >= x->slots;
+        for (int o = 0; o < t; o++) bad = bad || slots[t] == slots[o];
+    }
+    if (bad) {
+        set_error(g, "fused norm/RoPE scatter: not connected, bad slots or shape (%u rows, %u heads, %d ranks)",
+                  rows, heads, x->ranks);
+        return 0;
+    }
+    h3b::QkvRopeInput in{};
+    if (!rope_input(g, in, qkv, qn, kn, co, si, rows, heads, 128, rope_half, eps, grouped)) return 0;
+    void *window[3][16];
+    unsigned long long *flags[16];
+    for (int p = 0; p < x->ranks; p++) {
+        for (int t = 0; t < 3; t++) window[t][p] = x->mapped[p] + x->slot_bytes * slots[t];
+        flags[p] = reinterpret_cast<unsigned long long *>(x->mapped[p] + x->flags_offset);
+    }
+    int *status = nullptr;
+    if (!cuda_ok(g, h3b::device_status_word(&status))) return 0;
+    return cuda_ok(g, h3b::qkv_rope_head_shards(in, window[0], window[1], window[2], x->rank, x->ranks, g->stream)) &&
            cuda_ok(g, h3b::exchange_handshake(flags, ++x->epoch, status, x->rank, x->ranks, g->stream));
 }

@@ -130,6 +130,25 @@ int h3_gpu_cross_attention_bf16(h3_gpu *gpu, h3_gpu_tensor *out, size_t out_row,
                                 const h3_gpu_tensor *v, size_t kv_row, uint32_t query_rows,
                                 uint32_t key_rows, uint32_t heads);
 
+/* Q/K RMS-norm + rotary embedding on the fused QKV projection output, the producer of the
+ * attention inputs: h3_gpu.h:434-455 -> cuda/h3_gpu_cuda.cu:989-1031 (kernels
+ * cuda/primitives.cuh:897-962, cuda/fast_primitives.cuh:184-265). qkv is [sequence][3][heads][128]
+ * (grouped: [sequence][heads][3][128], the checkpoint's layout); q_norm, k_norm [128];
+ * rope_cos, rope_sin [sequence][rope_half]; query, key, value [sequence][heads][128]; all bf16.
+ * Results are bit-identical to the reference's kernels. head_dim must be 128 (the DiT's; the
+ * reference's generic kernel also takes other sizes), rope_half a multiple of 4, <= 64. */
+int h3_gpu_qkv_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key, h3_gpu_tensor *value,
+                         const h3_gpu_tensor *qkv, const h3_gpu_tensor *q_norm,
+                         const h3_gpu_tensor *k_norm, const h3_gpu_tensor *rope_cos,
+                         const h3_gpu_tensor *rope_sin, uint32_t sequence, uint32_t heads,
+                         uint32_t head_dim, uint32_t rope_half, float epsilon);
+int h3_gpu_grouped_qkv_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key,
+                                 h3_gpu_tensor *value, const h3_gpu_tensor *qkv,
+                                 const h3_gpu_tensor *q_norm, const h3_gpu_tensor *k_norm,
+                                 const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                                 uint32_t sequence, uint32_t heads, uint32_t head_dim,
+                                 uint32_t rope_half, float epsilon);
+
 /* Video sparse attention: cuda/h3_cuda.h:70-76 -> cuda/vsa.cuh:192-300. */
 h3_gpu_vsa *h3_gpu_vsa_new(h3_gpu *gpu, uint32_t text_rows, uint32_t audio_rows, uint32_t time,
                            uint32_t height, uint32_t width, uint32_t heads);
@@ -231,6 +250,18 @@ int h3b_exchange_sdpa_gather_bf16(h3b_exchange *exchange, int slot, const h3_gpu
                                   const h3_gpu_tensor *k, const h3_gpu_tensor *v, uint32_t sequence,
                                   uint32_t rows, uint32_t heads, float scale);
 
+/* The producer fused with the head scatter (no counterpart in the reference, which runs
+ * h3_gpu_grouped_qkv_rope_bf16 and then three h3_gpu_ulysses_scatter_heads_bf16 exchanges,
+ * h3_dit.c:2459-2462,2529-2538): this rank's `rows` rows of the QKV projection are normalised,
+ * rotated and stored directly into slots slot_q, slot_k, slot_v of the ranks that own each head,
+ * laid out [ranks*rows][heads/ranks][128] as the scatter leaves them; one kernel and one epoch
+ * handshake. rope_cos / rope_sin are this rank's [rows][rope_half] tables. */
+int h3b_exchange_qkv_rope_scatter_bf16(h3b_exchange *exchange, int slot_q, int slot_k, int slot_v,
+                                       const h3_gpu_tensor *qkv, const h3_gpu_tensor *q_norm,
+                                       const h3_gpu_tensor *k_norm, const h3_gpu_tensor *rope_cos,
+                                       const h3_gpu_tensor *rope_sin, uint32_t rows, uint32_t heads,
+                                       uint32_t rope_half, float epsilon, int grouped);
+
 /* VSA introspection for tests and tools: geometry, an override for the number of kept
  * video tiles (the reference fixes ceil(10 %)), and device pointers of the work buffers
  * of the last h3_gpu_vsa_bf16 call. which: 0 map, 1 sizes, 2-4 tiled q/k/v, 5 sparse out,
@@ -239,6 +270,16 @@ int h3b_vsa_info(const h3_gpu_vsa *vsa, int *rows, int *tiles, int *prefix, int 
 int h3b_vsa_set_keep(h3_gpu_vsa *vsa, int keep);
 int h3b_vsa_trace_scores(h3_gpu_vsa *vsa, int enable);
 void *h3b_vsa_buffer(const h3_gpu_vsa *vsa, int which);
+
+/* Video sparse attention fed by the QKV projection output instead of separate q, k, v
+ * (no counterpart in the reference, which runs h3_gpu_grouped_qkv_rope_bf16 and then
+ * h3_gpu_vsa_bf16): norm + rotation write q, k, v directly in tile order together with the
+ * tile means, so the token-major q, k, v are never materialised. Output and every work buffer
+ * equal those of h3_gpu_qkv_rope_bf16 followed by h3_gpu_vsa_bf16, bit for bit. */
+int h3b_vsa_qkv_rope_bf16(h3_gpu_vsa *vsa, h3_gpu_tensor *output, const h3_gpu_tensor *qkv,
+                          const h3_gpu_tensor *q_norm, const h3_gpu_tensor *k_norm,
+                          const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                          const h3_gpu_tensor *gate, uint32_t rope_half, float epsilon, int grouped);
 
 /* Top-k tile selection of video sparse attention with no device allocation at all. It has no
  * counterpart in the reference: it is for callers that cannot allocate where they call from -

@@ -584,6 +584,71 @@ ORACLE_API void oracle_vsa_untile_merge(uint16_t *output, const uint16_t *tiled,
 
 /* ---- Ulysses index algebra -------------------------------------------------- */
 
+/* ---- Q/K RMS-norm + rotary embedding (the producer of q, k, v) ---------------- */
+
+/*
+ * cuda/primitives.cuh:897-962 with head_dim == 128 (and cuda/fast_primitives.cuh:184-265,
+ * which the reference requires to be bit-identical to it). qkv: [rows][3][heads][128] or,
+ * grouped, [rows][heads][3][128]; weights [128]; cos/sin [rows][rope_half]; outputs
+ * [rows][heads][128]. Order of the sum of squares (:914-925): lane t of 32 chains fmaf over
+ * dimensions 4t..4t+3, then a shuffle-down tree 16,8,4,2,1 whose lane 0 is the sum.
+ * x * inverse * weight is rounded to bf16 (:935-939); dimension d < rope_half rotates with
+ * d + rope_half, each product rounded to bf16 before the subtraction / addition (:940-959).
+ * One deliberate difference: the GPU takes rsqrtf (an approximation, <= 2 ulp); this file
+ * uses 1/sqrtf, so single outputs may differ from the GPU by one bf16 ulp where that last
+ * bit of the inverse decides a rounding. Bit-level parity of the CUDA kernel is pinned
+ * against the reference's own kernel run on the same GPU instead.
+ */
+ORACLE_API void oracle_qkv_rope(uint16_t *query, uint16_t *key, uint16_t *value, const uint16_t *qkv,
+                                const uint16_t *q_weight, const uint16_t *k_weight,
+                                const uint16_t *rope_cos, const uint16_t *rope_sin, int rows,
+                                int heads, int rope_half, float epsilon, int grouped) {
+    const size_t inner = (size_t)heads * 128;
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < rows; row++)
+        for (int head = 0; head < heads; head++) {
+            size_t base[3];
+            base[0] = (size_t)row * inner * 3 + (size_t)head * 128;
+            base[1] = base[0] + inner;
+            base[2] = base[0] + inner * 2;
+            if (grouped) {
+                base[0] = (size_t)row * inner * 3 + (size_t)head * 128 * 3;
+                base[1] = base[0] + 128;
+                base[2] = base[1] + 128;
+            }
+            const size_t out = ((size_t)row * heads + head) * 128;
+            for (int which = 0; which < 2; which++) {
+                const uint16_t *x = qkv + base[which];
+                const uint16_t *w = which ? k_weight : q_weight;
+                uint16_t *y = (which ? key : query) + out;
+                float lanes[32];
+                for (int t = 0; t < 32; t++) {
+                    float sum = 0.0f;
+                    for (int d = 4 * t; d < 4 * t + 4; d++) sum = fmaf(bf16_to_f32(x[d]), bf16_to_f32(x[d]), sum);
+                    lanes[t] = sum;
+                }
+                const float inverse = 1.0f / sqrtf(shuffle_down(lanes, 0) / 128.0f + epsilon);
+                float normed[128];
+                for (int d = 0; d < 128; d++)
+                    normed[d] = bf16_round(bf16_to_f32(x[d]) * inverse * bf16_to_f32(w[d]));
+                for (int d = 0; d < 128; d++) {
+                    float r = normed[d];
+                    if (d < rope_half) {
+                        const float c = bf16_to_f32(rope_cos[(size_t)row * rope_half + d]);
+                        const float s = bf16_to_f32(rope_sin[(size_t)row * rope_half + d]);
+                        r = bf16_round(normed[d] * c) - bf16_round(normed[d + rope_half] * s);
+                    } else if (d < 2 * rope_half) {
+                        const float c = bf16_to_f32(rope_cos[(size_t)row * rope_half + d - rope_half]);
+                        const float s = bf16_to_f32(rope_sin[(size_t)row * rope_half + d - rope_half]);
+                        r = bf16_round(normed[d] * c) + bf16_round(normed[d - rope_half] * s);
+                    }
+                    y[d] = f32_to_bf16(r);
+                }
+            }
+            memcpy(value + out, qkv + base[2], 128 * sizeof(uint16_t));
+        }
+}
+
 /*
  * cuda/parallel.cuh:67-143. All ranks' buffers live in one address space here:
  * in: [ranks][rows][heads][dim] (rank r's row shard), out:

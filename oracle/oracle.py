@@ -194,6 +194,16 @@ def vsa_forward(q, k, v, gate, vmap, keep=None, round_p=True):
                 compression=comp, out=out)
 
 
+def qkv_rope(qkv, q_weight, k_weight, rope_cos, rope_sin, heads, rope_half, epsilon=1e-5, grouped=True):
+    """qkv: [rows, 3*heads*128] uint16 (bf16 bits). Returns q, k, v [rows, heads, 128]."""
+    qkv, q_weight, k_weight, rope_cos, rope_sin = _c(qkv, q_weight, k_weight, rope_cos, rope_sin)
+    rows = qkv.shape[0]
+    q, k, v = (np.empty((rows, heads, 128), dtype=np.uint16) for _ in range(3))
+    lib().oracle_qkv_rope(_p(q), _p(k), _p(v), _p(qkv), _p(q_weight), _p(k_weight), _p(rope_cos),
+                          _p(rope_sin), rows, heads, rope_half, C.c_float(epsilon), int(grouped))
+    return q, k, v
+
+
 def ulysses(x, inverse=False):
     """x: [ranks, rows, heads, dim] -> [ranks, ranks*rows, heads/ranks, dim] (or back)."""
     if not inverse:

@@ -39,7 +39,7 @@ def build_if_possible(force=False):
         return OUT
     OUT.parent.mkdir(exist_ok=True)
     ref = reference_root()
-    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", "-w", "-DH3_VSA",
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", "--fmad=false", "-w", "-DH3_VSA",
            "-Xcompiler", "-fPIC", "-shared", "-o", str(OUT), str(source), "-I", str(ref),
            "-I", str(ref / "cuda"), "-L", str(PRODUCT.parent), "-lh3b200_attn", "-lcublas",
            "-lcublasLt", "-lcudnn", "-lnccl", "-Xlinker", "-Bsymbolic", "-Xlinker",

@@ -114,6 +114,30 @@ def main():
         fused2 = gpu.read(slots[3], (rows, H, D))
         assert np.array_equal(fused2[:n], gathered[:n]), "attention with fused gather differs"
         assert gpu.device_status() == 0
+    # ---- norm + RoPE fused with the scatter: same bits as norm + RoPE followed by three scatters ----
+    half = 48
+    qkv = oracle.normal_bf16((world, rows, 3 * H * D), 77, 1.5)   # every rank's rows of the projection
+    rng = np.random.default_rng(5)
+    qw, kw = (oracle.to_bf16(1.0 + 0.2 * rng.standard_normal(D).astype(np.float32)) for _ in range(2))
+    angle = rng.uniform(0.0, 6.28, (world, rows, half)).astype(np.float32)
+    tin = [gpu.tensor(a) for a in (qkv[rank], qw, kw, oracle.to_bf16(np.cos(angle[rank])),
+                                   oracle.to_bf16(np.sin(angle[rank])))]
+    parts = [gpu.empty_bf16(rows * H * D) for _ in range(3)]
+    gpu.call("grouped_qkv_rope_bf16", *parts, *tin, rows, H, D, half, 1e-5)
+    unfused = []
+    for i, part in enumerate(parts):
+        assert lib.h3b_exchange_scatter_heads_bf16(x, i, part, rows, H, D), gpu.error()
+        unfused.append(gpu.read(slots[i], (world * rows, H // world, D)).copy())
+    for i in range(3):
+        gpu.call("zero", slots[i])
+    # every rank must have cleared its slots before any peer stores into them again
+    assert lib.h3b_exchange_gather_heads_bf16(x, 3, out2, rows, H, D), gpu.error()
+    gpu.submit()
+    assert lib.h3b_exchange_qkv_rope_scatter_bf16(x, 0, 1, 2, *tin, rows, H, half, C.c_float(1e-5), 1), gpu.error()
+    for i in range(3):
+        assert np.array_equal(gpu.read(slots[i], (world * rows, H // world, D)), unfused[i]), \
+            "fused norm/RoPE scatter differs (tensor %d)" % i
+    assert gpu.device_status() == 0
     for t in slots:
         lib.h3_gpu_tensor_free(t)
     lib.h3b_exchange_free(x)
