@@ -140,7 +140,7 @@ def main():
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="dense", choices=["dense", "vsa", "live"])
+    parser.add_argument("--workload", default="dense", choices=["dense", "vsa", "live", "producer"])
     parser.add_argument("--no-also", action="store_true", help="skip the secondary measurements")
     parser.add_argument("--exchange", default="push", choices=["push", "nccl"],
                         help="N>1: fused peer-memory exchange kernel (default) or transpose + NCCL send/recv")
@@ -418,9 +418,9 @@ def dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_o
     """One denoising step of the 50-block DiT at the benchmark shape, timed at N GPUs.
 
     Op order of the reference's run_block (h3_dit.c:2450-2673) with the reference's widths
-    (hidden 5376, FFN 14336, h3_dit.c:20-35) and the benchmark's 24 heads. Attention and the
-    Ulysses exchanges are this library's; the projections and MLP are torch bf16 GEMMs and the
-    elementwise ops (AdaLN, per-head RMS norm, SwiGLU, gates) are plain torch ops standing in for
+    (hidden 5376, FFN 14336, h3_dit.c:20-35) and the benchmark's 24 heads. Q/K norm + RoPE, attention
+    and the Ulysses exchanges are this library's; the projections and MLP are torch bf16 GEMMs and
+    the other elementwise ops (AdaLN, SwiGLU, gates) are plain torch ops standing in for
     the reference's own kernels, which are outside this library. One block's synthetic weights
     are reused for all blocks. Reported for the scaling picture only."""
     hidden, ffn, inner = 5376, 14336, HEADS * DIM
@@ -438,6 +438,8 @@ def dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_o
     gathered = torch.empty(world * rows, hidden, device=device, dtype=torch.bfloat16) if world > 1 else None
     wrap = lambda t: gpu.wrap(t.data_ptr(), t.numel())
     tq, tk, tv, to, tscr = wrap(q), wrap(k), wrap(v), wrap(o), wrap(scratch)
+    rope_tensors = rope_tables(torch, device, g, rows)   # kept alive: the wrappers do not own them
+    rope = [wrap(t) for t in rope_tensors]
     F = torch.nn.functional
     lib = gpu.lib
 
@@ -448,25 +450,26 @@ def dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_o
         x = x0.clone()
         for _ in range(blocks):
             h = norm_mod(x, mod[0], mod[1])
-            qkv = (h @ w_qkv).view(rows, 3, HEADS, DIM)
-            q.copy_(F.rms_norm(qkv[:, 0], (DIM,)))       # stands in for QK-RMS + RoPE writing Q, K, V
-            k.copy_(F.rms_norm(qkv[:, 1], (DIM,)))
-            v.copy_(qkv[:, 2])
+            qkv = h @ w_qkv                               # [rows][q|k|v][head][128]
+            tqkv = wrap(qkv)
             if exchange is not None:
-                for i, t in enumerate((tq, tk, tv)):
-                    if not lib.h3b_exchange_scatter_heads_bf16(exchange, i, t, rows, HEADS, DIM):
-                        raise RuntimeError(gpu.error())
+                # norm + RoPE store straight into the owners' head shards
+                if not lib.h3b_exchange_qkv_rope_scatter_bf16(exchange, 0, 1, 2, tqkv, *rope, rows, HEADS, 48,
+                                                              1e-5, 0):
+                    raise RuntimeError(gpu.error())
                 if not lib.h3b_exchange_sdpa_gather_bf16(exchange, 3, slots[0], slots[1], slots[2], plan.sequence,
                                                          rows, HEADS, SCALE):
                     raise RuntimeError(gpu.error())
                 gpu.call("copy_bf16", to, 0, slots[3], 0, rows * HEADS * DIM)   # window -> torch tensor
             else:
+                gpu.call("qkv_rope_bf16", tq, tk, tv, tqkv, *rope, rows, HEADS, DIM, 48, 1e-5)
                 if world > 1:
                     for t in (tq, tk, tv):
                         gpu.call("ulysses_scatter_heads_bf16", comm, t, tscr, rows, HEADS, DIM)
                 gpu.call("sdpa_bf16", to, tq, tk, tv, plan.sequence, local_heads, DIM, SCALE)
                 if world > 1:
                     gpu.call("ulysses_gather_heads_bf16", comm, to, tscr, rows, HEADS, DIM)
+            gpu.free(tqkv)
             x = x + mod[2] * (o.view(rows, inner) @ w_out)
             h = norm_mod(x, mod[3], mod[4])
             u = h @ w_fc1
@@ -487,8 +490,8 @@ def dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_o
     ms = max_over_ranks(a.elapsed_time(b) / steps)
     gemm_flops = 2.0 * plan.sequence * (hidden * 3 * inner + inner * hidden + hidden * 2 * ffn + ffn * hidden) * blocks
     attn_flops = 4.0 * plan.sequence ** 2 * HEADS * DIM * blocks
-    return {"workload": "50-block DiT denoising step, L=%d, H=%d, hidden %d, FFN %d; attention + Ulysses exchanges from "
-                        "this library, GEMMs and elementwise ops torch" % (plan.sequence, HEADS, hidden, ffn),
+    return {"workload": "50-block DiT denoising step, L=%d, H=%d, hidden %d, FFN %d; norm/RoPE, attention, Ulysses "
+                        "exchanges from this library; GEMMs and other elementwise ops torch" % (plan.sequence, HEADS, hidden, ffn),
             "ms_per_step": ms, "n_gpus": world, "steps": steps, "blocks": blocks,
             "model_tflops": (gemm_flops + attn_flops) / ms / 1e9}
 
@@ -518,6 +521,8 @@ def secondary(gpu, torch, device, stream, pk, only=None, steps=5):
         vsa_part(gpu, torch, device, pk, out, events, wrap, g)
     if only in (None, "live"):
         live_part(gpu, torch, device, out, events, wrap, g)
+    if only in (None, "producer"):
+        producer_part(gpu, torch, device, pk, out, events, wrap, g)
     return out
 
 
@@ -565,6 +570,61 @@ def vsa_part(gpu, torch, device, pk, out, events, wrap, g):
         "coarse_frac_of_hbm": coarse_bytes / (total_ms - fine_ms) / 1e6 / pk["hbm_gbs"],
     }
     lib.h3_gpu_vsa_free(vsa)
+
+
+def rope_tables(torch, device, g, rows, half=48):
+    angle = 6.2831853 * torch.rand(rows, half, generator=g, device=device)
+    weights = [(1.0 + 0.1 * torch.randn(DIM, generator=g, device=device)).to(torch.bfloat16) for _ in range(2)]
+    return weights[0], weights[1], torch.cos(angle).to(torch.bfloat16), torch.sin(angle).to(torch.bfloat16)
+
+
+def producer_part(gpu, torch, device, pk, out, events, wrap, g):
+    """Q/K norm + RoPE, the kernel that writes the attention inputs (HBM bound: every element
+    of q, k and v is read once and written once = 6 bytes per bf16 element)."""
+    lib = gpu.lib
+    g.manual_seed(1006)
+    rows, half = SEQ, 48
+    qkv = torch.randn(rows, 3 * HEADS * DIM, generator=g, device=device).to(torch.bfloat16)
+    qw, kw, co, si = rope_tables(torch, device, g, rows)
+    q, k, v = (torch.empty(rows, HEADS, DIM, device=device, dtype=torch.bfloat16) for _ in range(3))
+    tin = [wrap(t) for t in (qkv, qw, kw, co, si)]
+    touts = [wrap(t) for t in (q, k, v)]
+    ms = events(lambda: gpu.call("grouped_qkv_rope_bf16", *touts, *tin, rows, HEADS, DIM, half, 1e-5), 10, 3)
+    traffic = 6.0 * rows * HEADS * DIM * 2
+    result = {"workload": "grouped QKV norm + RoPE, L=%d, H=%d, rope_half %d" % (rows, HEADS, half),
+              "token_major_ms": ms, "gbs": traffic / ms / 1e6, "frac_of_hbm_peak": traffic / ms / 1e6 / pk["hbm_gbs"],
+              "algorithmic_bytes": traffic}
+    del qkv, q, k, v
+    # VSA fed by the projection output: one fused pass instead of norm/RoPE + tile gather
+    text, audio, grid = 64, 512, ((32, 30, 54) if SEQ == 52352 else (8, 30, 54))   # small case for profiling
+    vsa = gpu.call("vsa_new", text, audio, *grid, HEADS)
+    info = [C.c_int() for _ in range(4)]
+    lib.h3b_vsa_info(vsa, *[C.byref(x) for x in info])
+    rows, tiles, prefix, _ = (x.value for x in info)
+    lib.h3b_vsa_set_keep(vsa, (tiles - prefix) // 8)
+    qkv = torch.randn(rows, 3 * HEADS * DIM, generator=g, device=device).to(torch.bfloat16)
+    qw, kw, co, si = rope_tables(torch, device, g, rows)
+    q, k, v, o = (torch.empty(rows, HEADS, DIM, device=device, dtype=torch.bfloat16) for _ in range(4))
+    gate = (0.3 * torch.randn(rows, HEADS, DIM, generator=g, device=device)).to(torch.bfloat16)
+    tin = [wrap(t) for t in (qkv, qw, kw, co, si)]
+    tq, tk, tv, to, tg = (wrap(t) for t in (q, k, v, o, gate))
+
+    def two_calls():
+        gpu.call("grouped_qkv_rope_bf16", tq, tk, tv, *tin, rows, HEADS, DIM, half, 1e-5)
+        if not lib.h3_gpu_vsa_bf16(vsa, to, tq, tk, tv, tg):
+            raise RuntimeError(gpu.error())
+
+    def fused():
+        if not lib.h3b_vsa_qkv_rope_bf16(vsa, to, *tin, tg, half, 1e-5, 1):
+            raise RuntimeError(gpu.error())
+
+    # alternate the two variants: the fine stage runs at the power cap and drifts with temperature
+    rounds = [(events(two_calls), events(fused)) for _ in range(3)]
+    result["vsa_norm_rope_then_vsa_ms"] = sum(r[0] for r in rounds) / len(rounds)
+    result["vsa_fed_by_projection_ms"] = sum(r[1] for r in rounds) / len(rounds)
+    result["vsa_rounds_ms"] = rounds
+    lib.h3_gpu_vsa_free(vsa)
+    out["producer"] = result
 
 
 def live_part(gpu, torch, device, out, events, wrap, g):

@@ -14,6 +14,8 @@
 // Every kernel here is bound by HBM traffic: 6 bytes moved per bf16 element of q, k and v.
 #include <algorithm>
 
+#include <cuda_bf16.h>
+
 #include "attn_kernels.h"
 #include "sm100_ptx.cuh"
 
@@ -22,7 +24,6 @@ namespace {
 
 constexpr int RD = 128;        // head dimension
 constexpr int TILE_ROWS = 64;  // rows of a VSA tile
-constexpr int TILE_HEADS = 2;  // heads per CTA of the tile sink (96 KB of staging, two CTAs per SM)
 
 struct RopeArgs {
     const uint16_t *qkv, *q_weight, *k_weight, *rope_cos, *rope_sin;
@@ -39,24 +40,20 @@ struct RopeArgs {
 
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
-__device__ __forceinline__ float round_bf16(float x) {
-    return __bfloat162float(__float2bfloat16_rn(x));
-}
 __device__ __forceinline__ void unpack4(uint2 raw, float (&x)[4]) {
     x[0] = bf16_lo(raw.x);
     x[1] = bf16_hi(raw.x);
     x[2] = bf16_lo(raw.y);
     x[3] = bf16_hi(raw.y);
 }
-__device__ __forceinline__ uint32_t bits2(float lo, float hi) {
-    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(lo)) |
-           ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(hi)) << 16);
-}
 
 // What a lane needs that does not depend on the head: norm weights, its rotation partner and
-// the row's angles.
+// the row's angles. The sine carries the sign of the rotation (minus for dimensions below
+// rope_half), so both halves compute round(y cos) + round(z sin'); a - b and a + (-b) are the
+// same IEEE operation and negation commutes with rounding.
 struct LaneSetup {
-    float qw[4], kw[4], c[4], s[4];
+    float qw[4], kw[4];
+    uint2 c, s;   // four cosines / signed sines of the row, packed bf16
     unsigned partner;
     int role;   // 0: dimension d < rope_half, 1: rope_half <= d < 2 rope_half, 2: not rotated
 };
@@ -67,18 +64,39 @@ __device__ __forceinline__ void lane_weights(const RopeArgs &a, unsigned lane, L
     const unsigned quarter = a.rope_half / 4;
     u.role = lane < quarter ? 0 : lane < 2 * quarter ? 1 : 2;
     u.partner = u.role == 0 ? lane + quarter : u.role == 1 ? lane - quarter : lane;
+    u.c = u.s = make_uint2(0u, 0u);
 }
-__device__ __forceinline__ void lane_angles(const RopeArgs &a, unsigned lane, size_t row, LaneSetup &u) {
+// The row's four cosines and sines of this lane, still packed (lanes that do not rotate: zeros).
+__device__ __forceinline__ void load_angles(const RopeArgs &a, unsigned lane, const LaneSetup &u, size_t row,
+                                            uint2 &c, uint2 &s) {
+    c = s = make_uint2(0u, 0u);
     if (u.role == 2) return;
     const size_t angle = row * a.rope_half + (u.role == 0 ? lane * 4 : lane * 4 - a.rope_half);
-    unpack4(__ldg(reinterpret_cast<const uint2 *>(a.rope_cos + angle)), u.c);
-    unpack4(__ldg(reinterpret_cast<const uint2 *>(a.rope_sin + angle)), u.s);
+    c = __ldg(reinterpret_cast<const uint2 *>(a.rope_cos + angle));
+    s = __ldg(reinterpret_cast<const uint2 *>(a.rope_sin + angle));
+}
+__device__ __forceinline__ void set_angles(LaneSetup &u, uint2 c, uint2 s) {
+    u.c = c;
+    if (u.role == 0) {   // flip the sign bits of the four sines
+        s.x ^= 0x80008000u;
+        s.y ^= 0x80008000u;
+    }
+    u.s = s;
+}
+// Products of two bf16 values rounded to bf16, a pair at a time. The exact product of two
+// 8-bit significands has 16 bits, so the reference's fp32 product is exact and its rounding to
+// bf16 is the single rounding mul.rn.bf16x2 performs.
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
 }
 
 // One vector of 128 values across the warp. Explicit _rn intrinsics: no contraction may merge
 // a product with the add that follows it, each product is rounded on its own as in the
-// reference build (--fmad=false).
-__device__ __forceinline__ uint2 norm_rope(uint2 raw, const float (&w)[4], const LaneSetup &u, float epsilon) {
+// reference build (--fmad=false). Roundings to bf16 go two at a time through cvt.rn.bf16x2.
+__device__ __forceinline__ uint2 norm_rope(uint2 raw, const float (&w)[4], const LaneSetup &u, float epsilon,
+                                           bool rotate) {
     float x[4];
     unpack4(raw, x);
     float sum = 0.0f;
@@ -88,21 +106,21 @@ __device__ __forceinline__ uint2 norm_rope(uint2 raw, const float (&w)[4], const
     for (int distance = 16; distance; distance >>= 1)
         sum = __fadd_rn(sum, __shfl_down_sync(0xffffffffu, sum, distance));
     sum = __shfl_sync(0xffffffffu, sum, 0);
-    const float inverse = rsqrtf(__fadd_rn(__fdiv_rn(sum, (float)RD), epsilon));
-    float y[4], z[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) y[i] = round_bf16(__fmul_rn(__fmul_rn(x[i], inverse), w[i]));
-#pragma unroll
-    for (int i = 0; i < 4; i++) z[i] = __shfl_sync(0xffffffffu, y[i], u.partner);
-    if (u.role != 2) {
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float mine = round_bf16(__fmul_rn(y[i], u.c[i]));
-            const float other = round_bf16(__fmul_rn(z[i], u.s[i]));
-            y[i] = u.role == 0 ? __fsub_rn(mine, other) : __fadd_rn(mine, other);
-        }
-    }
-    return make_uint2(bits2(y[0], y[1]), bits2(y[2], y[3]));
+    // sum / 128 as a multiplication: the same correctly rounded value for every input
+    const float inverse = rsqrtf(__fadd_rn(__fmul_rn(sum, 1.0f / (float)RD), epsilon));
+    uint2 y;   // normalised, weighted, rounded to bf16
+    y.x = pack_bf16(__fmul_rn(__fmul_rn(x[0], inverse), w[0]), __fmul_rn(__fmul_rn(x[1], inverse), w[1]));
+    y.y = pack_bf16(__fmul_rn(__fmul_rn(x[2], inverse), w[2]), __fmul_rn(__fmul_rn(x[3], inverse), w[3]));
+    if (!rotate) return y;   // rope_half == 0: uniform over the launch
+    uint2 z;
+    z.x = __shfl_sync(0xffffffffu, y.x, u.partner);
+    z.y = __shfl_sync(0xffffffffu, y.y, u.partner);
+    if (u.role == 2) return y;
+    const uint32_t m01 = mul_bf16x2(y.x, u.c.x), m23 = mul_bf16x2(y.y, u.c.y);
+    const uint32_t o01 = mul_bf16x2(z.x, u.s.x), o23 = mul_bf16x2(z.y, u.s.y);
+    y.x = pack_bf16(__fadd_rn(bf16_lo(m01), bf16_lo(o01)), __fadd_rn(bf16_hi(m01), bf16_hi(o01)));
+    y.y = pack_bf16(__fadd_rn(bf16_lo(m23), bf16_lo(o23)), __fadd_rn(bf16_hi(m23), bf16_hi(o23)));
+    return y;
 }
 
 // Offsets (in uint2 units) of the q, k, v vectors of (row, head) inside the projection output:
@@ -120,132 +138,158 @@ __device__ __forceinline__ void input_offsets(const RopeArgs &a, size_t row, uns
     }
 }
 
-// One warp per row, walking its heads two at a time (six 256-byte loads in flight per warp).
+// One warp per (row, chunk of up to eight heads), four heads (twelve 256-byte loads) in flight
+// per pass; the chunks keep warps short so the last wave of CTAs drains evenly.
 // PEER: stores go to the window of the rank that owns the head.
+constexpr unsigned HEAD_CHUNK = 8, HEADS_IN_FLIGHT = 4;
+
 template <bool PEER>
 __global__ void __launch_bounds__(256)
 qkv_rope_rows_kernel(const RopeArgs a) {
     const unsigned lane = threadIdx.x & 31;
-    const size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (row >= a.rows) return;   // whole warps leave
+    const unsigned chunks = (a.heads + HEAD_CHUNK - 1) / HEAD_CHUNK;
+    const size_t item = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (item >= (size_t)a.rows * chunks) return;   // whole warps leave
+    const size_t row = item / chunks;
+    const unsigned first = (unsigned)(item % chunks) * HEAD_CHUNK, last = min(a.heads, first + HEAD_CHUNK);
+    const bool rotate = a.rope_half != 0;
     LaneSetup u;
     lane_weights(a, lane, u);
-    lane_angles(a, lane, row, u);
+    uint2 craw, sraw;
+    load_angles(a, lane, u, row, craw, sraw);
     const uint2 *in = reinterpret_cast<const uint2 *>(a.qkv);
     const unsigned per_rank = PEER ? a.heads / a.ranks : a.heads;
-    auto store = [&](unsigned head, uint2 q, uint2 k, uint2 v) {
-        size_t at;
-        uint2 *dst[3];
-        if (PEER) {
-            const unsigned owner = head / per_rank;
-            at = (((size_t)a.rank * a.rows + row) * per_rank + head % per_rank) * (RD / 4) + lane;
+    bool angles_set = false;
+    for (unsigned head = first; head < last; head += HEADS_IN_FLIGHT) {
+        uint2 raw[HEADS_IN_FLIGHT][3];
 #pragma unroll
-            for (int t = 0; t < 3; t++) dst[t] = reinterpret_cast<uint2 *>(a.peer[t][owner]);
-        } else {
-            at = (row * a.heads + head) * (RD / 4) + lane;
+        for (unsigned h = 0; h < HEADS_IN_FLIGHT; h++)
+            if (head + h < last) {
+                size_t off[3];
+                input_offsets(a, row, head + h, off);
 #pragma unroll
-            for (int t = 0; t < 3; t++) dst[t] = reinterpret_cast<uint2 *>(a.out[t]);
+                for (int t = 0; t < 3; t++) raw[h][t] = __ldcs(in + off[t] + lane);
+            }
+        if (!angles_set) {
+            set_angles(u, craw, sraw);
+            angles_set = true;
         }
-        dst[0][at] = q;
-        dst[1][at] = k;
-        dst[2][at] = v;
-    };
-    unsigned head = 0;
-    for (; head + 1 < a.heads; head += 2) {
-        size_t o0[3], o1[3];
-        input_offsets(a, row, head, o0);
-        input_offsets(a, row, head + 1, o1);
-        const uint2 q0 = __ldg(in + o0[0] + lane), k0 = __ldg(in + o0[1] + lane), v0 = __ldg(in + o0[2] + lane);
-        const uint2 q1 = __ldg(in + o1[0] + lane), k1 = __ldg(in + o1[1] + lane), v1 = __ldg(in + o1[2] + lane);
-        store(head, norm_rope(q0, u.qw, u, a.epsilon), norm_rope(k0, u.kw, u, a.epsilon), v0);
-        store(head + 1, norm_rope(q1, u.qw, u, a.epsilon), norm_rope(k1, u.kw, u, a.epsilon), v1);
-    }
-    if (head < a.heads) {
-        size_t o0[3];
-        input_offsets(a, row, head, o0);
-        const uint2 q0 = __ldg(in + o0[0] + lane), k0 = __ldg(in + o0[1] + lane), v0 = __ldg(in + o0[2] + lane);
-        store(head, norm_rope(q0, u.qw, u, a.epsilon), norm_rope(k0, u.kw, u, a.epsilon), v0);
+#pragma unroll
+        for (unsigned h = 0; h < HEADS_IN_FLIGHT; h++)
+            if (head + h < last) {
+                const uint2 q = norm_rope(raw[h][0], u.qw, u, a.epsilon, rotate);
+                const uint2 k = norm_rope(raw[h][1], u.kw, u, a.epsilon, rotate);
+                size_t at;
+                uint2 *dst[3];
+                if (PEER) {
+                    const unsigned owner = (head + h) / per_rank;
+                    at = (((size_t)a.rank * a.rows + row) * per_rank + (head + h) % per_rank) * (RD / 4) + lane;
+#pragma unroll
+                    for (int t = 0; t < 3; t++) dst[t] = reinterpret_cast<uint2 *>(a.peer[t][owner]);
+                } else {
+                    at = (row * a.heads + head + h) * (RD / 4) + lane;
+#pragma unroll
+                    for (int t = 0; t < 3; t++) dst[t] = reinterpret_cast<uint2 *>(a.out[t]);
+                }
+                __stcs(dst[0] + at, q);
+                __stcs(dst[1] + at, k);
+                __stcs(dst[2] + at, raw[h][2]);
+            }
     }
 }
 
-// One CTA per (tile, pair of heads): the 64 token rows the tile map names are normalised and
-// rotated, written in tile order, and kept in shared memory for the tile means, which follow
-// the summation order of the tile-pooling kernel (cuda/vsa.cuh:18-43): row i feeds accumulator
-// (i % 4, (i / 4) % 4); the four accumulators of a lane are added left to right, then
-// (lane0 + lane2) + (lane1 + lane3), then divided by the number of valid rows.
+// One CTA per (tile, head): the 64 token rows the tile map names are normalised and rotated and
+// written in tile order; the tile means follow the summation order of the tile-pooling kernel
+// (cuda/vsa.cuh:18-43): row i feeds accumulator i % 16, in the order i = a, a + 16, a + 32,
+// a + 48; accumulators a = l, l + 4, l + 8, l + 12 are added left to right into lane sum l, the
+// mean is ((lane0 + lane2) + (lane1 + lane3)) / valid rows.
+// Warp w owns accumulators w and w + 8: for each it requests its four rows (twelve vectors and
+// their angles) at once, then works through them in order, so the sums stay in registers and
+// only the sixteen partial sums per tensor meet in shared memory. The kernel issues about as
+// many instructions as the two kernels it replaces; what it saves is their memory round trip.
 __global__ void __launch_bounds__(256)
 qkv_rope_tiles_kernel(const RopeArgs a) {
-    extern __shared__ uint2 staged[];   // [tensor][slot][head of the pair][32 lanes]
+    __shared__ float4 partial[16][3][32];   // [accumulator][tensor][lane]
     __shared__ int rows[TILE_ROWS];
-    const int tile = blockIdx.x, head0 = blockIdx.y * TILE_HEADS;
+    const int tile = blockIdx.x, head = blockIdx.y;
     const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (threadIdx.x < TILE_ROWS) rows[threadIdx.x] = a.map[tile * TILE_ROWS + threadIdx.x];
     __syncthreads();
+    const bool rotate = a.rope_half != 0;
     LaneSetup u;
     lane_weights(a, lane, u);
     const uint2 *in = reinterpret_cast<const uint2 *>(a.qkv);
-    const int pair = min(TILE_HEADS, (int)a.heads - head0);
-    for (int slot = warp; slot < TILE_ROWS; slot += 8) {
-        const int row = rows[slot];   // the same for the whole warp
-        if (row >= 0) lane_angles(a, lane, (size_t)row, u);
-        for (int h = 0; h < pair; h++) {
-            uint2 r[3] = {make_uint2(0u, 0u), make_uint2(0u, 0u), make_uint2(0u, 0u)};
-            if (row >= 0) {
-                size_t off[3];
-                input_offsets(a, (size_t)row, head0 + h, off);
-                const uint2 q = __ldg(in + off[0] + lane), k = __ldg(in + off[1] + lane);
-                r[2] = __ldg(in + off[2] + lane);
-                r[0] = norm_rope(q, u.qw, u, a.epsilon);
-                r[1] = norm_rope(k, u.kw, u, a.epsilon);
-            }
-            const size_t at = (((size_t)(head0 + h) * a.tiles + tile) * TILE_ROWS + slot) * (RD / 4) + lane;
 #pragma unroll
-            for (int t = 0; t < 3; t++) {
-                reinterpret_cast<uint2 *>(a.tiled[t])[at] = r[t];
-                staged[((t * TILE_ROWS + slot) * TILE_HEADS + h) * 32 + lane] = r[t];
-            }
-        }
-    }
-    __syncthreads();
-    // tile means: thread = (tensor, head of the pair, four dimensions)
-    const int item = threadIdx.x >> 5;   // 0 .. 3 * TILE_HEADS - 1 are used
-    if (item >= 3 * TILE_HEADS) return;
-    const int t = item / TILE_HEADS, h = item % TILE_HEADS;
-    if (h >= pair) return;
-    float lane_sum[4][4];
-#pragma unroll
-    for (int l = 0; l < 4; l++) {
-        float acc[4][4];
-#pragma unroll
-        for (int slot = 0; slot < 4; slot++)
-#pragma unroll
-            for (int d = 0; d < 4; d++) acc[slot][d] = 0.0f;
+    for (int which = 0; which < 2; which++) {
+        const int acc_id = warp + 8 * which;
+        uint2 raw[4][3], craw[4], sraw[4];
+        int row[4];
 #pragma unroll
         for (int round = 0; round < 4; round++) {
+            row[round] = rows[acc_id + 16 * round];   // the same for the whole warp
 #pragma unroll
-            for (int slot = 0; slot < 4; slot++) {
-                const int i = l + slot * 4 + round * 16;
-                const uint2 x = staged[((t * TILE_ROWS + i) * TILE_HEADS + h) * 32 + lane];
-                acc[slot][0] = __fadd_rn(acc[slot][0], bf16_lo(x.x));
-                acc[slot][1] = __fadd_rn(acc[slot][1], bf16_hi(x.x));
-                acc[slot][2] = __fadd_rn(acc[slot][2], bf16_lo(x.y));
-                acc[slot][3] = __fadd_rn(acc[slot][3], bf16_hi(x.y));
+            for (int t = 0; t < 3; t++) raw[round][t] = make_uint2(0u, 0u);
+            craw[round] = sraw[round] = make_uint2(0u, 0u);
+            if (row[round] >= 0) {
+                size_t off[3];
+                input_offsets(a, (size_t)row[round], head, off);
+#pragma unroll
+                for (int t = 0; t < 3; t++) raw[round][t] = __ldcs(in + off[t] + lane);
+                load_angles(a, lane, u, (size_t)row[round], craw[round], sraw[round]);
+            }
+        }
+        float acc[3][4];
+#pragma unroll
+        for (int t = 0; t < 3; t++)
+#pragma unroll
+            for (int d = 0; d < 4; d++) acc[t][d] = 0.0f;
+#pragma unroll
+        for (int round = 0; round < 4; round++) {
+            if (row[round] >= 0) {
+                set_angles(u, craw[round], sraw[round]);
+                raw[round][0] = norm_rope(raw[round][0], u.qw, u, a.epsilon, rotate);
+                raw[round][1] = norm_rope(raw[round][1], u.kw, u, a.epsilon, rotate);
+            }
+            const size_t at = (((size_t)head * a.tiles + tile) * TILE_ROWS + acc_id + 16 * round) * (RD / 4) + lane;
+#pragma unroll
+            for (int t = 0; t < 3; t++) {
+                __stcs(reinterpret_cast<uint2 *>(a.tiled[t]) + at, raw[round][t]);
+                acc[t][0] = __fadd_rn(acc[t][0], bf16_lo(raw[round][t].x));
+                acc[t][1] = __fadd_rn(acc[t][1], bf16_hi(raw[round][t].x));
+                acc[t][2] = __fadd_rn(acc[t][2], bf16_lo(raw[round][t].y));
+                acc[t][3] = __fadd_rn(acc[t][3], bf16_hi(raw[round][t].y));
             }
         }
 #pragma unroll
-        for (int d = 0; d < 4; d++)
-            lane_sum[l][d] = __fadd_rn(__fadd_rn(__fadd_rn(acc[0][d], acc[1][d]), acc[2][d]), acc[3][d]);
+        for (int t = 0; t < 3; t++)
+            partial[acc_id][t][lane] = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
+    }
+    __syncthreads();
+    // tile means: warp = tensor, lane = four dimensions
+    if (warp >= 3) return;
+    const int t = warp;
+    float4 lane_sum[4];
+#pragma unroll
+    for (int l = 0; l < 4; l++) {
+        float4 s4 = partial[l][t][lane];
+#pragma unroll
+        for (int slot = 1; slot < 4; slot++) {
+            const float4 x = partial[l + 4 * slot][t][lane];
+            s4.x = __fadd_rn(s4.x, x.x);
+            s4.y = __fadd_rn(s4.y, x.y);
+            s4.z = __fadd_rn(s4.z, x.z);
+            s4.w = __fadd_rn(s4.w, x.w);
+        }
+        lane_sum[l] = s4;
     }
     const float size = (float)a.sizes[tile];
     float4 mean;
-    mean.x = __fdiv_rn(__fadd_rn(__fadd_rn(lane_sum[0][0], lane_sum[2][0]), __fadd_rn(lane_sum[1][0], lane_sum[3][0])), size);
-    mean.y = __fdiv_rn(__fadd_rn(__fadd_rn(lane_sum[0][1], lane_sum[2][1]), __fadd_rn(lane_sum[1][1], lane_sum[3][1])), size);
-    mean.z = __fdiv_rn(__fadd_rn(__fadd_rn(lane_sum[0][2], lane_sum[2][2]), __fadd_rn(lane_sum[1][2], lane_sum[3][2])), size);
-    mean.w = __fdiv_rn(__fadd_rn(__fadd_rn(lane_sum[0][3], lane_sum[2][3]), __fadd_rn(lane_sum[1][3], lane_sum[3][3])), size);
-    reinterpret_cast<float4 *>(a.pooled[t])[((size_t)(head0 + h) * a.tiles + tile) * (RD / 4) + lane] = mean;
+    mean.x = __fdiv_rn(__fadd_rn(__fadd_rn(lane_sum[0].x, lane_sum[2].x), __fadd_rn(lane_sum[1].x, lane_sum[3].x)), size);
+    mean.y = __fdiv_rn(__fadd_rn(__fadd_rn(lane_sum[0].y, lane_sum[2].y), __fadd_rn(lane_sum[1].y, lane_sum[3].y)), size);
+    mean.z = __fdiv_rn(__fadd_rn(__fadd_rn(lane_sum[0].z, lane_sum[2].z), __fadd_rn(lane_sum[1].z, lane_sum[3].z)), size);
+    mean.w = __fdiv_rn(__fadd_rn(__fadd_rn(lane_sum[0].w, lane_sum[2].w), __fadd_rn(lane_sum[1].w, lane_sum[3].w)), size);
+    reinterpret_cast<float4 *>(a.pooled[t])[((size_t)head * a.tiles + tile) * (RD / 4) + lane] = mean;
 }
-
-constexpr size_t TILES_SMEM = (size_t)3 * TILE_ROWS * TILE_HEADS * 32 * sizeof(uint2);
 
 cudaError_t fill(RopeArgs &a, const QkvRopeInput &in) {
     if (!in.qkv || !in.q_weight || !in.k_weight || !in.rope_cos || !in.rope_sin || !in.rows ||
@@ -266,6 +310,11 @@ cudaError_t fill(RopeArgs &a, const QkvRopeInput &in) {
     return cudaSuccess;
 }
 
+unsigned rows_grid(const QkvRopeInput &in) {
+    const size_t items = (size_t)in.rows * ((in.heads + HEAD_CHUNK - 1) / HEAD_CHUNK);
+    return (unsigned)((items + 7) / 8);
+}
+
 }  // namespace
 
 cudaError_t qkv_rope_token_major(const QkvRopeInput &in, void *q, void *k, void *v, cudaStream_t stream) {
@@ -278,7 +327,7 @@ cudaError_t qkv_rope_token_major(const QkvRopeInput &in, void *q, void *k, void 
         if (reinterpret_cast<uintptr_t>(out[t]) % 8) return cudaErrorMisalignedAddress;
         a.out[t] = static_cast<uint16_t *>(out[t]);
     }
-    qkv_rope_rows_kernel<false><<<(in.rows + 7) / 8, 256, 0, stream>>>(a);
+    qkv_rope_rows_kernel<false><<<rows_grid(in), 256, 0, stream>>>(a);
     return cudaGetLastError();
 }
 
@@ -297,7 +346,7 @@ cudaError_t qkv_rope_head_shards(const QkvRopeInput &in, void *const window_q[],
     }
     a.rank = (unsigned)rank;
     a.ranks = (unsigned)ranks;
-    qkv_rope_rows_kernel<true><<<(in.rows + 7) / 8, 256, 0, stream>>>(a);
+    qkv_rope_rows_kernel<true><<<rows_grid(in), 256, 0, stream>>>(a);
     return cudaGetLastError();
 }
 
@@ -315,18 +364,8 @@ cudaError_t qkv_rope_vsa_tiles(const QkvRopeInput &in, const int *map, const int
     a.map = map;
     a.sizes = sizes;
     a.tiles = tiles;
-    static thread_local int configured_device = -1;
-    int device = 0;
-    e = cudaGetDevice(&device);
-    if (e != cudaSuccess) return e;
-    if (configured_device != device) {
-        e = cudaFuncSetAttribute(qkv_rope_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)TILES_SMEM);
-        if (e != cudaSuccess) return e;
-        configured_device = device;
-    }
-    dim3 grid(tiles, (in.heads + TILE_HEADS - 1) / TILE_HEADS);
-    qkv_rope_tiles_kernel<<<grid, 256, TILES_SMEM, stream>>>(a);
+    dim3 grid(tiles, in.heads);
+    qkv_rope_tiles_kernel<<<grid, 256, 0, stream>>>(a);
     return cudaGetLastError();
 }
 
