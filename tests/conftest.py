@@ -59,3 +59,35 @@ def assert_attention_close(got_bf16_as_f32, want_f32, max_abs=1e-2, cosine=0.999
     assert m["cosine"] >= cosine, m
     assert m["rel_l2"] <= rel_l2, m
     return m
+
+
+ROPE_HALF = 48   # reference h3_dit.c:32
+
+
+def rope_inputs(oracle, rows, heads, seed):
+    """Seeded inputs of the Q/K norm + RoPE operator: projection output, norm weights, angles."""
+    qkv = oracle.normal_bf16((rows, 3 * heads * 128), seed, 1.5)
+    rng = np.random.default_rng(seed)
+    qw = oracle.to_bf16(1.0 + 0.2 * rng.standard_normal(128).astype(np.float32))
+    kw = oracle.to_bf16(1.0 + 0.2 * rng.standard_normal(128).astype(np.float32))
+    angle = rng.uniform(0.0, 2.0 * np.pi, (rows, ROPE_HALF)).astype(np.float32)
+    return qkv, qw, kw, oracle.to_bf16(np.cos(angle)), oracle.to_bf16(np.sin(angle))
+
+
+def bf16_step_distance(a, b):
+    """Distance in bf16 steps between two arrays of bf16 bit patterns."""
+    def ordered(x):
+        x = x.astype(np.int32)
+        return np.where(x & 0x8000, -(x & 0x7fff), x & 0x7fff)
+    return np.abs(ordered(a) - ordered(b))
+
+
+def assert_rope_close(oracle, got, want):
+    """Two results of the norm + RoPE operator that differ only in the last bit of the inverse
+    root mean square (the GPU's approximate rsqrt against 1/sqrtf): few elements differ; where
+    no rotation follows, by one bf16 step; where one follows, by one step of either product
+    (values reach about 8: steps of 2^-5), however small the rotated difference is."""
+    d = bf16_step_distance(got, want)
+    assert (d != 0).mean() < 2e-3, "too many elements differ"
+    assert d[..., 2 * ROPE_HALF:].max() <= 1, "more than one bf16 step"
+    assert np.abs(oracle.from_bf16(got) - oracle.from_bf16(want))[..., :2 * ROPE_HALF].max() <= 2.0 ** -4

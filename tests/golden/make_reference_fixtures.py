@@ -5,6 +5,7 @@
 Uses oracle/_ref/libh3_ref_cuda.so (the reference's cuda/h3_gpu_cuda.cu compiled unmodified,
 see oracle/ref_build.py). Everything stored here is computed by REFERENCE code:
   reference_sdpa_f32.npz : FP32 fallback attention (cuda/h3_gpu_cuda.cu:1131-1180) on F32 tensors
+  reference_qkv_rope.npz : Q/K norm + RoPE (cuda/fast_primitives.cuh:184-265), both input layouts
   reference_vsa_*.npz    : tile map, sizes, tiled Q, pooled means (tile_pool), pooled scores after
                            the in-place softmax (cuBLAS SGEMM + pooled_softmax), index lists and
                            counts (select_blocks), compression (cuBLAS SGEMM)
@@ -20,9 +21,13 @@ ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests"))
 import __graft_entry__ as entry  # noqa: E402
+import ctypes as C  # noqa: E402
+
+from conftest import ROPE_HALF, rope_inputs  # noqa: E402
 from refbackend import Reference, ref_vsa_buffers  # noqa: E402
 
 SDPA_CASE = dict(L=130, H=2, seed=31)
+ROPE_CASE = dict(rows=37, heads=5, seed=61)
 VSA_CASES = [dict(text=3, audio=11, shape=(1, 2, 3), heads=2, seed=700),
              dict(text=65, audio=67, shape=(5, 7, 9), heads=2, seed=710),
              dict(text=17, audio=30, shape=(7, 8, 8), heads=3, seed=720)]
@@ -42,6 +47,17 @@ def main(out_dir):
     y = ref.empty(q.size, f32=True)
     ref.check(ref.lib.h3_gpu_sdpa_f32(ref.gpu, y, ref.tensor(q), ref.tensor(k), ref.tensor(v), c["L"], c["H"], 128, scale), "sdpa_f32")
     np.savez_compressed(out_dir / "reference_sdpa_f32.npz", out=ref.read(y, q.shape, f32=True), **c)
+    c = ROPE_CASE
+    inputs = rope_inputs(oracle, c["rows"], c["heads"], c["seed"])
+    stored = dict(c)
+    for name in ("qkv_rope_bf16", "grouped_qkv_rope_bf16"):
+        outs = [ref.empty(c["rows"] * c["heads"] * 128) for _ in range(3)]
+        fn = getattr(ref.lib, "h3_gpu_" + name)
+        fn.argtypes = [C.c_void_p] * 9 + [C.c_uint32] * 4 + [C.c_float]
+        ref.check(fn(ref.gpu, *outs, *[ref.tensor(x) for x in inputs], c["rows"], c["heads"], 128, ROPE_HALF, 1e-5), name)
+        for which, t in zip("qkv", outs):
+            stored[name + "_" + which] = ref.read(t, (c["rows"], c["heads"], 128))
+    np.savez_compressed(out_dir / "reference_qkv_rope.npz", **stored)
     for n, c in enumerate(VSA_CASES):
         vmap = oracle.VsaMap(c["text"], c["audio"], *c["shape"])
         T, H = vmap.tiles, c["heads"]

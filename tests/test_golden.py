@@ -2,7 +2,7 @@
 
 tests/golden/reference_*.npz were produced on a B200 by tests/golden/make_reference_fixtures.py
 from the reference's unmodified cuda/h3_gpu_cuda.cu (FP32 fallback attention, tile_pool, cuBLAS
-pooled scores + pooled_softmax, select_blocks, cuBLAS compression). They pin the restatement in
+pooled scores + pooled_softmax, select_blocks, cuBLAS compression, Q/K norm + RoPE). They pin the restatement in
 oracle/h3_attention_oracle.c: integer and order-pinned stages bit for bit, cuBLAS-ordered
 floating-point stages to FP32 rounding.
 """
@@ -11,7 +11,21 @@ from pathlib import Path
 import numpy as np
 import pytest
 
+from conftest import ROPE_HALF, assert_rope_close, rope_inputs
+
 GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+@pytest.mark.parametrize("name,grouped", [("qkv_rope_bf16", False), ("grouped_qkv_rope_bf16", True)])
+def test_qkv_rope_matches_reference_kernel(oracle, name, grouped):
+    """The reference computes the inverse root mean square with the GPU's approximate rsqrt, the
+    oracle with 1/sqrtf: equal except where that last bit decides a bf16 rounding."""
+    g = np.load(GOLDEN / "reference_qkv_rope.npz")
+    rows, heads, seed = int(g["rows"]), int(g["heads"]), int(g["seed"])
+    q, k, v = oracle.qkv_rope(*rope_inputs(oracle, rows, heads, seed), heads, ROPE_HALF, 1e-5, grouped)
+    assert np.array_equal(v, g[name + "_v"])
+    assert_rope_close(oracle, q, g[name + "_q"])
+    assert_rope_close(oracle, k, g[name + "_k"])
 
 
 def test_fp32_attention_matches_reference_fallback(oracle):

@@ -15,18 +15,11 @@ import ctypes as C
 import numpy as np
 import pytest
 
+from conftest import ROPE_HALF, assert_rope_close, rope_inputs
 from refbackend import REF_LIB, Reference
 
-HALF = 48   # h3_dit.c:32
-
-
-def make_inputs(oracle, rows, heads, seed, grouped=True):
-    qkv = oracle.normal_bf16((rows, 3 * heads * 128), seed, 1.5)
-    rng = np.random.default_rng(seed)
-    qw = oracle.to_bf16(1.0 + 0.2 * rng.standard_normal(128).astype(np.float32))
-    kw = oracle.to_bf16(1.0 + 0.2 * rng.standard_normal(128).astype(np.float32))
-    angle = rng.uniform(0.0, 2.0 * np.pi, (rows, HALF)).astype(np.float32)
-    return qkv, qw, kw, oracle.to_bf16(np.cos(angle)), oracle.to_bf16(np.sin(angle))
+HALF = ROPE_HALF
+make_inputs = rope_inputs
 
 
 def float64_restatement(oracle, qkv, qw, kw, co, si, heads, grouped):
@@ -58,14 +51,6 @@ def test_oracle_matches_float64_mathematics(oracle, grouped):
     assert np.abs(oracle.from_bf16(q)[..., 2 * HALF:] - wq[..., 2 * HALF:]).max() < 0.04
 
 
-def bf16_ulp_distance(a, b):
-    """Distance in bf16 steps between two bf16 bit arrays (sign-magnitude -> ordered ints)."""
-    def ordered(x):
-        x = x.astype(np.int32)
-        return np.where(x & 0x8000, -(x & 0x7fff), x & 0x7fff)
-    return np.abs(ordered(a) - ordered(b))
-
-
 def run_ours(gpu, name, qkv, qw, kw, co, si, rows, heads):
     tensors = [gpu.tensor(x) for x in (qkv, qw, kw, co, si)]
     outs = [gpu.empty_bf16(rows * heads * 128) for _ in range(3)]
@@ -85,14 +70,8 @@ def test_kernel_against_oracle(gpu, oracle, rows, heads, grouped):
     q, k, v = run_ours(gpu, name, qkv, qw, kw, co, si, rows, heads)
     wq, wk, wv = oracle.qkv_rope(qkv, qw, kw, co, si, heads, HALF, 1e-5, grouped)
     assert np.array_equal(v, wv)
-    for got, want in ((q, wq), (k, wk)):
-        d = bf16_ulp_distance(got, want)
-        assert (d != 0).mean() < 2e-3, "too many elements differ from the oracle"
-        # not rotated: the one rounding may flip, one bf16 step
-        assert d[..., 2 * HALF:].max() <= 1, "more than one bf16 step from the oracle"
-        # rotated: a flipped rounding of either product moves the difference of the two by one
-        # step OF THE PRODUCT (values reach ~8: steps of 2^-5), however small the difference is
-        assert np.abs(oracle.from_bf16(got) - oracle.from_bf16(want))[..., :2 * HALF].max() <= 2.0 ** -4
+    assert_rope_close(oracle, q, wq)
+    assert_rope_close(oracle, k, wk)
 
 
 @pytest.mark.gpu
