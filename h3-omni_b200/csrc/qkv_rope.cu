@@ -139,12 +139,14 @@ __device__ __forceinline__ void input_offsets(const RopeArgs &a, size_t row, uns
 }
 
 // One warp per (row, chunk of up to eight heads), four heads (twelve 256-byte loads) in flight
-// per pass; the chunks keep warps short so the last wave of CTAs drains evenly.
+// per pass; the chunks keep warps short so the last wave of CTAs drains evenly. Registers are
+// capped at 64 for four CTAs per SM: at three the kernel reached 82 % of the HBM copy rate, at
+// four 92 %.
 // PEER: stores go to the window of the rank that owns the head.
 constexpr unsigned HEAD_CHUNK = 8, HEADS_IN_FLIGHT = 4;
 
 template <bool PEER>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 qkv_rope_rows_kernel(const RopeArgs a) {
     const unsigned lane = threadIdx.x & 31;
     const unsigned chunks = (a.heads + HEAD_CHUNK - 1) / HEAD_CHUNK;
@@ -203,11 +205,11 @@ qkv_rope_rows_kernel(const RopeArgs a) {
 // (cuda/vsa.cuh:18-43): row i feeds accumulator i % 16, in the order i = a, a + 16, a + 32,
 // a + 48; accumulators a = l, l + 4, l + 8, l + 12 are added left to right into lane sum l, the
 // mean is ((lane0 + lane2) + (lane1 + lane3)) / valid rows.
-// Warp w owns accumulators w and w + 8: for each it requests its four rows (twelve vectors and
-// their angles) at once, then works through them in order, so the sums stay in registers and
-// only the sixteen partial sums per tensor meet in shared memory. The kernel issues about as
+// Warp w owns accumulators w and w + 8 and works through their rows in order, two rows requested
+// at a time, so the sums stay in registers and only the sixteen partial sums per tensor meet in
+// shared memory; registers are capped for four CTAs per SM (occupancy hides the gather latency). The kernel issues about as
 // many instructions as the two kernels it replaces; what it saves is their memory round trip.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 qkv_rope_tiles_kernel(const RopeArgs a) {
     __shared__ float4 partial[16][3][32];   // [accumulator][tensor][lane]
     __shared__ int rows[TILE_ROWS];
@@ -222,42 +224,46 @@ qkv_rope_tiles_kernel(const RopeArgs a) {
 #pragma unroll
     for (int which = 0; which < 2; which++) {
         const int acc_id = warp + 8 * which;
-        uint2 raw[4][3], craw[4], sraw[4];
-        int row[4];
-#pragma unroll
-        for (int round = 0; round < 4; round++) {
-            row[round] = rows[acc_id + 16 * round];   // the same for the whole warp
-#pragma unroll
-            for (int t = 0; t < 3; t++) raw[round][t] = make_uint2(0u, 0u);
-            craw[round] = sraw[round] = make_uint2(0u, 0u);
-            if (row[round] >= 0) {
-                size_t off[3];
-                input_offsets(a, (size_t)row[round], head, off);
-#pragma unroll
-                for (int t = 0; t < 3; t++) raw[round][t] = __ldcs(in + off[t] + lane);
-                load_angles(a, lane, u, (size_t)row[round], craw[round], sraw[round]);
-            }
-        }
         float acc[3][4];
 #pragma unroll
         for (int t = 0; t < 3; t++)
 #pragma unroll
             for (int d = 0; d < 4; d++) acc[t][d] = 0.0f;
 #pragma unroll
-        for (int round = 0; round < 4; round++) {
-            if (row[round] >= 0) {
-                set_angles(u, craw[round], sraw[round]);
-                raw[round][0] = norm_rope(raw[round][0], u.qw, u, a.epsilon, rotate);
-                raw[round][1] = norm_rope(raw[round][1], u.kw, u, a.epsilon, rotate);
-            }
-            const size_t at = (((size_t)head * a.tiles + tile) * TILE_ROWS + acc_id + 16 * round) * (RD / 4) + lane;
+        for (int half = 0; half < 2; half++) {   // two rows (six vectors and their angles) requested at once
+            uint2 raw[2][3], craw[2], sraw[2];
+            int row[2];
 #pragma unroll
-            for (int t = 0; t < 3; t++) {
-                __stcs(reinterpret_cast<uint2 *>(a.tiled[t]) + at, raw[round][t]);
-                acc[t][0] = __fadd_rn(acc[t][0], bf16_lo(raw[round][t].x));
-                acc[t][1] = __fadd_rn(acc[t][1], bf16_hi(raw[round][t].x));
-                acc[t][2] = __fadd_rn(acc[t][2], bf16_lo(raw[round][t].y));
-                acc[t][3] = __fadd_rn(acc[t][3], bf16_hi(raw[round][t].y));
+            for (int i = 0; i < 2; i++) {
+                row[i] = rows[acc_id + 16 * (2 * half + i)];   // the same for the whole warp
+#pragma unroll
+                for (int t = 0; t < 3; t++) raw[i][t] = make_uint2(0u, 0u);
+                craw[i] = sraw[i] = make_uint2(0u, 0u);
+                if (row[i] >= 0) {
+                    size_t off[3];
+                    input_offsets(a, (size_t)row[i], head, off);
+#pragma unroll
+                    for (int t = 0; t < 3; t++) raw[i][t] = __ldcs(in + off[t] + lane);
+                    load_angles(a, lane, u, (size_t)row[i], craw[i], sraw[i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                if (row[i] >= 0) {
+                    set_angles(u, craw[i], sraw[i]);
+                    raw[i][0] = norm_rope(raw[i][0], u.qw, u, a.epsilon, rotate);
+                    raw[i][1] = norm_rope(raw[i][1], u.kw, u, a.epsilon, rotate);
+                }
+                const size_t at =
+                    (((size_t)head * a.tiles + tile) * TILE_ROWS + acc_id + 16 * (2 * half + i)) * (RD / 4) + lane;
+#pragma unroll
+                for (int t = 0; t < 3; t++) {
+                    __stcs(reinterpret_cast<uint2 *>(a.tiled[t]) + at, raw[i][t]);
+                    acc[t][0] = __fadd_rn(acc[t][0], bf16_lo(raw[i][t].x));
+                    acc[t][1] = __fadd_rn(acc[t][1], bf16_hi(raw[i][t].x));
+                    acc[t][2] = __fadd_rn(acc[t][2], bf16_lo(raw[i][t].y));
+                    acc[t][3] = __fadd_rn(acc[t][3], bf16_hi(raw[i][t].y));
+                }
             }
         }
 #pragma unroll
