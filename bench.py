@@ -31,7 +31,7 @@ SEQ_VIDEO, SEQ_AUDIO, HEADS, DIM = 51840, 512, 24, 128
 SEQ = SEQ_VIDEO + SEQ_AUDIO
 SCALE = float(1.0 / np.sqrt(128.0))
 EXCHANGE_NOTE = "fused peer-memory push kernels; gather fused into the attention epilogue"
-E2E_HEAD_GROUPS = 6   # head groups of the pipelined host-buffer call (4 heads each at H=24)
+E2E_HEAD_GROUPS = int(os.environ.get("H3B_E2E_GROUPS", "6"))   # head groups of the pipelined host-buffer call (4 heads each at H=24)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dense kernel: the ncu capture
 # summarised in profiles/ measured 384.8 MB at L=16,384, H=24 (algorithmic 402.7 MB; part of the
 # output was still in L2 at kernel end); traffic grows with L*H, so per row of one head:
@@ -302,7 +302,7 @@ def main():
             if not lib.h3b_sdpa_bf16_host(gpu.gpu, host_o.data_ptr(), host_q.data_ptr(), host_k.data_ptr(),
                                           host_v.data_ptr(), SEQ, HEADS, DIM, SCALE, E2E_HEAD_GROUPS):
                 raise RuntimeError(gpu.error())
-            launches[0] += E2E_HEAD_GROUPS
+            launches[0] += E2E_HEAD_GROUPS + (2 if HEADS // E2E_HEAD_GROUPS >= 2 else 0)   # edge groups run as two halves
             return
         dq.copy_(host_q, non_blocking=True)
         dk.copy_(host_k, non_blocking=True)

@@ -501,18 +501,36 @@ extern "C" int h3b_sdpa_bf16_host(h3_gpu *g, uint16_t *out, const uint16_t *q, c
         return 0;
     }
     const uint32_t hg = heads / head_groups;
-    const size_t row_bytes = (size_t)hg * 256, pitch = (size_t)heads * 256;
-    if (!pipeline_prepare(g, row_bytes * sequence)) return 0;
+    const size_t pitch = (size_t)heads * 256;
+    if (!pipeline_prepare(g, (size_t)hg * 256 * sequence)) return 0;
     host_pipeline &p = g->pipe;
+    // The first and the last group are cut in two: the copy-in before the first kernel and the
+    // copy-out after the last one are the only transfers nothing overlaps, so they are made short.
+    uint32_t first_head[66], head_count[66];
+    uint32_t chunks = 0;
+    if (head_groups > 64) {
+        set_error(g, "host attention: at most 64 head groups");
+        return 0;
+    }
+    for (uint32_t group = 0; group < head_groups; group++) {
+        const bool edge = (group == 0 || group + 1 == head_groups) && hg >= 2;
+        const uint32_t parts = edge ? 2 : 1, base = group * hg;
+        for (uint32_t part = 0; part < parts; part++) {
+            first_head[chunks] = base + (part ? hg / 2 : 0);
+            head_count[chunks++] = parts == 1 ? hg : part ? hg - hg / 2 : hg / 2;
+        }
+    }
     // everything already queued on the context's stream comes first
     if (!cuda_ok(g, cudaEventRecord(p.computed[0], g->stream)) ||
         !cuda_ok(g, cudaStreamWaitEvent(p.h2d, p.computed[0], 0)))
         return 0;
-    for (uint32_t group = 0; group < head_groups; group++) {
-        const int s = group & 1;
-        const size_t offset = (size_t)group * hg * 128;   // elements into a host row
-        if (group >= 2) {
-            // slot reuse: inputs after the kernel of group-2, output after its copy-out
+    for (uint32_t chunk = 0; chunk < chunks; chunk++) {
+        const int s = chunk & 1;
+        const uint32_t n = head_count[chunk];
+        const size_t offset = (size_t)first_head[chunk] * 128;   // elements into a host row
+        const size_t row_bytes = (size_t)n * 256;
+        if (chunk >= 2) {
+            // slot reuse: inputs after the kernel of chunk-2, output after its copy-out
             if (!cuda_ok(g, cudaStreamWaitEvent(p.h2d, p.computed[s], 0)) ||
                 !cuda_ok(g, cudaStreamWaitEvent(g->stream, p.stored[s], 0)))
                 return 0;
@@ -525,7 +543,7 @@ extern "C" int h3b_sdpa_bf16_host(h3_gpu *g, uint16_t *out, const uint16_t *q, c
         if (!cuda_ok(g, cudaEventRecord(p.loaded[s], p.h2d)) ||
             !cuda_ok(g, cudaStreamWaitEvent(g->stream, p.loaded[s], 0)) ||
             !cuda_ok(g, h3_flash3_bf16(p.slot[s][3], p.slot[s][0], p.slot[s][1], p.slot[s][2], nullptr,
-                                       1, sequence, hg, hg, scale, g->stream)) ||
+                                       1, sequence, n, n, scale, g->stream)) ||
             !cuda_ok(g, cudaEventRecord(p.computed[s], g->stream)) ||
             !cuda_ok(g, cudaStreamWaitEvent(p.d2h, p.computed[s], 0)) ||
             !cuda_ok(g, cudaMemcpy2DAsync(out + offset, pitch, p.slot[s][3], row_bytes, row_bytes,

@@ -207,7 +207,9 @@ int h3b_cross_attention_segments_bf16(h3_gpu *gpu, h3_gpu_tensor *out, size_t ou
  * [sequence][heads][128] bf16 in host memory (pinned for full speed). The heads are cut into
  * head_groups groups (heads % head_groups == 0) and copy-in, kernel and copy-out of
  * consecutive groups overlap on three streams, so the call costs about
- * max(copy time, kernel time). Synchronous: returns when `out` is complete. */
+ * max(copy time, kernel time); the first and the last group run as two halves to shorten the
+ * two transfers nothing can overlap. head_groups <= 64. Synchronous: returns when `out` is
+ * complete. */
 int h3b_sdpa_bf16_host(h3_gpu *gpu, uint16_t *out, const uint16_t *q, const uint16_t *k,
                        const uint16_t *v, uint32_t sequence, uint32_t heads, uint32_t head_dim,
                        float scale, uint32_t head_groups);
