@@ -604,6 +604,8 @@ struct h3_gpu_vsa {
     h3_gpu *gpu{};
     int rows{}, heads{}, tiles{}, prefix{}, keep{};
     bool trace_scores{};
+    cudaEvent_t stage[5]{};   // optional stage timing: before pooling, after pooling, selection, fine stage, merge
+    bool time_stages{};
     h3_gpu_tensor *map{}, *sizes{}, *q{}, *k{}, *v{}, *out{};
     h3_gpu_tensor *poolq{}, *poolk{}, *poolv{}, *scores{}, *compression{}, *indices{}, *counts{};
 };
@@ -613,6 +615,8 @@ extern "C" void h3_gpu_vsa_free(h3_gpu_vsa *s) {
     for (auto *t : {s->map, s->sizes, s->q, s->k, s->v, s->out, s->poolq, s->poolk, s->poolv,
                     s->scores, s->compression, s->indices, s->counts})
         h3_gpu_tensor_free(t);
+    for (cudaEvent_t e : s->stage)
+        if (e) cudaEventDestroy(e);
     delete s;
 }
 
@@ -714,12 +718,34 @@ extern "C" int h3b_vsa_trace_scores(h3_gpu_vsa *s, int enable) {
     s->trace_scores = enable != 0;
     return 1;
 }
+// Stage timing with CUDA events on the context's stream (off by default).
+extern "C" int h3b_vsa_time_stages(h3_gpu_vsa *s, int enable) {
+    if (!s) return 0;
+    if (enable)
+        for (cudaEvent_t &e : s->stage)
+            if (!e && !cuda_ok(s->gpu, cudaEventCreate(&e))) return 0;
+    s->time_stages = enable != 0;
+    return 1;
+}
+// Milliseconds of the last call's four stages: pooling (or norm + RoPE + pooling), scores +
+// selection + compression, block-sparse attention, merge. Waits for that call to finish.
+extern "C" int h3b_vsa_stage_ms(h3_gpu_vsa *s, float *ms) {
+    if (!s || !ms || !s->time_stages) return 0;
+    if (!cuda_ok(s->gpu, cudaEventSynchronize(s->stage[4]))) return 0;
+    for (int i = 0; i < 4; i++)
+        if (!cuda_ok(s->gpu, cudaEventElapsedTime(&ms[i], s->stage[i], s->stage[i + 1]))) return 0;
+    return 1;
+}
 extern "C" void *h3b_vsa_buffer(const h3_gpu_vsa *s, int which) {
     if (!s) return nullptr;
     const h3_gpu_tensor *all[] = {s->map, s->sizes, s->q, s->k, s->v, s->out, s->poolq, s->poolk,
                                   s->poolv, s->indices, s->counts, s->compression, s->scores};
     if (which < 0 || which >= (int)(sizeof all / sizeof all[0]) || !all[which]) return nullptr;
     return all[which]->data;
+}
+
+static int vsa_mark(h3_gpu_vsa *s, int which) {
+    return !s->time_stages || cuda_ok(s->gpu, cudaEventRecord(s->stage[which], s->gpu->stream));
 }
 
 // Everything after the tiled copies and tile means exist: scores + selection + compression,
@@ -729,6 +755,7 @@ static int vsa_after_tiling(h3_gpu_vsa *s, h3_gpu_tensor *out, const h3_gpu_tens
     float *pooled[3] = {(float *)s->poolq->data, (float *)s->poolk->data, (float *)s->poolv->data};
     const int *map = (const int *)s->map->data;
     const float scale = 1.0f / sqrtf(128.0f);
+    if (!vsa_mark(s, 1)) return 0;
     if (!cuda_ok(g, h3b::vsa_score_select_compress(
                         pooled[0], pooled[1], pooled[2],
                         s->trace_scores ? (float *)s->scores->data : nullptr,
@@ -736,13 +763,16 @@ static int vsa_after_tiling(h3_gpu_vsa *s, h3_gpu_tensor *out, const h3_gpu_tens
                         (float *)s->compression->data, s->tiles, s->prefix, s->keep, s->heads, scale,
                         g->stream)))
         return 0;
+    if (!vsa_mark(s, 2)) return 0;
     if (!cuda_ok(g, h3_vsa_hopper(s->out->data, s->q->data, s->k->data, s->v->data, nullptr,
                                   (int *)s->indices->data, (int *)s->counts->data,
                                   (int *)s->sizes->data, s->tiles, s->heads, g->stream)))
         return 0;
+    if (!vsa_mark(s, 3)) return 0;
     return cuda_ok(g, h3b::vsa_untile_merge(out->data, s->out->data, gate->data,
                                             (const float *)s->compression->data, map, s->tiles,
-                                            s->heads, g->stream));
+                                            s->heads, g->stream)) &&
+           vsa_mark(s, 4);
 }
 
 
@@ -760,6 +790,7 @@ extern "C" int h3_gpu_vsa_bf16(h3_gpu_vsa *s, h3_gpu_tensor *out, const h3_gpu_t
     void *tiled[3] = {s->q->data, s->k->data, s->v->data};
     float *pooled[3] = {(float *)s->poolq->data, (float *)s->poolk->data, (float *)s->poolv->data};
     const int *map = (const int *)s->map->data, *sizes = (const int *)s->sizes->data;
+    if (!vsa_mark(s, 0)) return 0;
     if (!cuda_ok(g, h3b::vsa_tile_pool3(src, tiled, pooled, map, sizes, s->tiles, s->heads, 3,
                                         g->stream)))
         return 0;
@@ -781,6 +812,7 @@ extern "C" int h3b_vsa_qkv_rope_bf16(h3_gpu_vsa *s, h3_gpu_tensor *out, const h3
         return 0;
     void *tiled[3] = {s->q->data, s->k->data, s->v->data};
     float *pooled[3] = {(float *)s->poolq->data, (float *)s->poolk->data, (float *)s->poolv->data};
+    if (!vsa_mark(s, 0)) return 0;
     if (!cuda_ok(g, h3b::qkv_rope_vsa_tiles(in, (const int *)s->map->data, (const int *)s->sizes->data,
                                             s->tiles, tiled, pooled, g->stream)))
         return 0;

@@ -272,6 +272,11 @@ int h3b_vsa_info(const h3_gpu_vsa *vsa, int *rows, int *tiles, int *prefix, int 
 int h3b_vsa_set_keep(h3_gpu_vsa *vsa, int keep);
 int h3b_vsa_trace_scores(h3_gpu_vsa *vsa, int enable);
 void *h3b_vsa_buffer(const h3_gpu_vsa *vsa, int which);
+/* Optional stage timing (CUDA events on the context's stream, off by default): after a call,
+ * h3b_vsa_stage_ms waits for it and returns the milliseconds of its four stages: pooling (or
+ * norm + RoPE + pooling), scores + selection + compression, block-sparse attention, merge. */
+int h3b_vsa_time_stages(h3_gpu_vsa *vsa, int enable);
+int h3b_vsa_stage_ms(h3_gpu_vsa *vsa, float *ms4);
 
 /* Video sparse attention fed by the QKV projection output instead of separate q, k, v
  * (no counterpart in the reference, which runs h3_gpu_grouped_qkv_rope_bf16 and then
