@@ -57,9 +57,6 @@ struct PairKvMaps {
 struct PairParams {
     int segments, seg_rows[PAIR_MAX_SEGMENTS];
     int lq, lk, heads, kv_heads;
-    // work units: `pair_units` CTAs own two query tiles, the CTAs after them one tile each
-    // (the two tiles of pair unit pair_units + i / 2); units_x pair units cover one head
-    int units_x, pair_units;
     float scale, scale_log2;
     __nv_bfloat16 *out;
     float *lse;
@@ -91,17 +88,9 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     auto bar_p_full = [&](int t) { return bar0 + 8u * (1 + 2 * ST + 2 + t); };
     auto bar_pv_done = [&](int t) { return bar0 + 8u * (1 + 2 * ST + 4 + t); };
 
-    // One tile per CTA ("single") where a second tile would only idle or would leave most SMs
-    // idle in the last wave; a row's arithmetic is the same in both forms, so results do not
-    // depend on which form computed them.
-    const int cta = blockIdx.x;
-    const bool tail_single = cta >= p.pair_units;
-    const int unit = tail_single ? p.pair_units + (cta - p.pair_units) / 2 : cta;
-    const int head = (unit / p.units_x) % p.heads, batch = unit / (p.units_x * p.heads);
+    const int head = blockIdx.y, batch = blockIdx.z;
     const int kv_head = head / (p.heads / p.kv_heads);
-    const int q_row0 = (unit % p.units_x) * 2 * PBM + (tail_single ? ((cta - p.pair_units) & 1) * PBM : 0);
-    const bool single = tail_single || q_row0 + PBM >= p.lq;   // no second tile to work on
-    if (tail_single && q_row0 >= p.lq) return;   // second half of a pair whose second tile does not exist
+    const int q_row0 = blockIdx.x * 2 * PBM;
     int n_tiles = 0;   // key tiles over all segments
     for (int s = 0; s < p.segments; s++) n_tiles += (p.seg_rows[s] + PBN - 1) / PBN;
 
@@ -134,8 +123,8 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             tma_prefetch_desc(&map_q);
-            mbar_arrive_expect_tx(bar_q_full, single ? PAIR_Q_BYTES / 2 : PAIR_Q_BYTES);
-            for (int t = 0; t < (single ? 1 : 2); t++) {
+            mbar_arrive_expect_tx(bar_q_full, PAIR_Q_BYTES);
+            for (int t = 0; t < 2; t++) {
                 const uint32_t dst = q_smem + t * (PAIR_Q_BYTES / 2);
                 tma_load_4d(dst, &map_q, bar_q_full, 0, head, q_row0 + t * PBM, batch);
                 tma_load_4d(dst + PAIR_HALF_BYTES, &map_q, bar_q_full, 64, head, q_row0 + t * PBM, batch);
@@ -207,7 +196,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             if (alive) {
                 tc5_fence_after();
                 issue_qk(0, 0);
-                if (!single) issue_qk(0, 1);
+                issue_qk(0, 1);
                 mma_commit(bar_empty(0));
             }
             for (int j = 0; alive && j < n_tiles; j++) {
@@ -242,18 +231,18 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     issue_qk(j + 1, 0);
                     TRACE_ADD(5);
                 }
-                if (!single) {
 #ifndef H3B_EXP_NO_PWAIT
+                {
                     TRACE_T0();
                     if (!mbar_wait(bar_p_full(1), j & 1, &abort_word)) break;
                     TRACE_ADD(3);
-#endif
-                    tc5_fence_after();
-                    issue_pv(j, 1);
                 }
+#endif
+                tc5_fence_after();
+                issue_pv(j, 1);
                 mma_commit(bar_empty((2 * j + 1) % ST));
                 if (more) {
-                    if (!single) issue_qk(j + 1, 1);
+                    issue_qk(j + 1, 1);
                     mma_commit(bar_empty((2 * j + 2) % ST));
                 }
             }
@@ -276,7 +265,6 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         // ------------------------------ online softmax ------------------------------
         const int t = warp >> 2;                // which query tile
         const int r = tid & 127;                // row inside the tile == TMEM lane
-        const int steps = (single && t == 1) ? 0 : n_tiles;   // a single-tile CTA has no tile B
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t s_addr = tmem + lane_base + t * PBN;
         const uint32_t o_addr = tmem + lane_base + PAIR_O_COL + t * PHD;
@@ -287,7 +275,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const long long trace_begin = clock64();
 #endif
         int seg = 0, seg_tile = 0;   // which segment, which tile of it, step j is
-        for (int j = 0; j < steps; j++) {
+        for (int j = 0; j < n_tiles; j++) {
             while (seg_tile * PBN >= p.seg_rows[seg]) {
                 seg++;
                 seg_tile = 0;
@@ -411,8 +399,8 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #endif
 
         // -------- epilogue: O / l -> bf16, straight to global memory --------
-        if (alive && steps) alive = __all_sync(0xffffffffu, mbar_wait(bar_pv_done(t), (n_tiles - 1) & 1, &abort_word));
-        if (alive && steps) {
+        if (alive) alive = __all_sync(0xffffffffu, mbar_wait(bar_pv_done(t), (n_tiles - 1) & 1, &abort_word));
+        if (alive) {
             tc5_fence_after();
             const float inv = 1.0f / l;
             const int row = q_row0 + t * PBM + r;
@@ -507,21 +495,8 @@ cudaError_t attn_dense_tc5_pair(const CUtensorMap_st *mq, const CUtensorMap_st *
         p.rank = peer->rank;
         p.total_heads = peer->total_heads;
     }
-    // Work units. If the last wave of two-tile CTAs would fill at most half of the SMs, its
-    // units run as twice as many one-tile CTAs instead (each takes about 0.7 of a two-tile CTA).
-    static thread_local int sms = 0;
-    if (!sms) {
-        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-        if (e != cudaSuccess) return e;
-    }
-    p.units_x = (int)((lq + 2 * PBM - 1) / (2 * PBM));
-    const long long units = (long long)p.units_x * heads * batch;
-    if (units > 0x3fffffff) return cudaErrorInvalidValue;
-    const int tail = (int)(units % sms);
-    const bool split_tail = units > sms && tail > 0 && 2 * tail <= sms;
-    p.pair_units = (int)units - (split_tail ? tail : 0);
-    const unsigned ctas = (unsigned)p.pair_units + (split_tail ? 2u * tail : 0u);
-    attn_tc5_pair_kernel<<<ctas, PAIR_THREADS, PAIR_SMEM_BYTES, stream>>>(*mq, kv, p);
+    dim3 grid((lq + 2 * PBM - 1) / (2 * PBM), heads, batch);
+    attn_tc5_pair_kernel<<<grid, PAIR_THREADS, PAIR_SMEM_BYTES, stream>>>(*mq, kv, p);
     return cudaGetLastError();
 }
 
