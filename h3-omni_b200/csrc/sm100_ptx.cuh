@@ -75,7 +75,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
-// Warp-collective bounded wait: lane 0 polls, the warp gets the verdict. 32x fewer probes of
+// Warp-collective bounded wait: lane 0 polls, the warp gets the result. 32x fewer probes of
 // the mbarrier word than every lane polling for itself - the probes go to shared memory,
 // which the tensor core is reading its operands from at the same time.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_word) {
