@@ -279,3 +279,66 @@ def test_segmented_live_attention_equals_concatenated(gpu, oracle, nq, ranges, H
         assert np.abs(oracle.from_bf16(got[2:]) - oracle.from_bf16(concat)).max() <= 4e-3
     assert gpu.device_status() == 0
     assert not gpu.lib.h3b_cross_attention_segments_bf16(gpu.gpu, out, 2, tq, 9, nq, H, 7, tk, tv, offs, rows)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_shapes_against_oracle(gpu, oracle, seed):
+    """Seeded random shapes around the tile boundaries of both tcgen05 kernels (128-row query
+    tiles, 256-row CTA pairs, 128-row key tiles): a dense call, a rectangular call with row
+    offsets, a causal/GQA call and a segmented call per seed, each against the oracle."""
+    rng = np.random.default_rng(1000 + seed)
+    near = lambda: int(rng.choice([1, 64, 127, 128, 129, 255, 256, 257, 383, 384, 385, 511, 640]) + rng.integers(0, 3))
+    H = int(rng.choice([1, 2, 3, 5]))
+    # dense
+    L = near()
+    got, want = run_sdpa(gpu, oracle, L, H, 3000 + seed)
+    assert_attention_close(got, want[0])
+    # rectangular with offsets
+    nq, nk, qo, ko, oo = near(), near(), int(rng.integers(0, 5)), int(rng.integers(0, 5)), int(rng.integers(0, 5))
+    q = oracle.normal_bf16((nq + qo, H, 128), 3100 + seed)
+    k = oracle.normal_bf16((nk + ko, H, 128), 3200 + seed)
+    v = oracle.normal_bf16((nk + ko, H, 128), 3300 + seed)
+    out = gpu.tensor(np.zeros((nq + oo, H, 128), dtype=np.uint16))
+    tq, tk, tv = gpu.tensor(q), gpu.tensor(k), gpu.tensor(v)
+    gpu.call("cross_attention_bf16", out, oo, tq, qo, tk, tv, ko, nq, nk, H)
+    got = gpu.read(out, (nq + oo, H, 128))
+    assert not got[:oo].any()
+    want, _ = oracle.attention(q[None, qo:], k[None, ko:], v[None, ko:], SCALE)
+    assert_attention_close(oracle.from_bf16(got[oo:]), want[0])
+    for t in (out, tq, tk, tv):
+        gpu.free(t)
+    # causal / grouped-query (the FlashAttention-2 adapter)
+    KH = int(rng.choice([1, 2]))
+    Hq = KH * int(rng.choice([1, 2, 3]))
+    causal = bool(rng.integers(0, 2))
+    Lc = near()
+    q = oracle.normal_bf16((1, Lc, Hq, 128), 3400 + seed)
+    k = oracle.normal_bf16((1, Lc, KH, 128), 3500 + seed)
+    v = oracle.normal_bf16((1, Lc, KH, 128), 3600 + seed)
+    ty, tq, tk, tv = gpu.empty_bf16(q.size), gpu.tensor(q), gpu.tensor(k), gpu.tensor(v)
+    data = gpu.lib.h3b_tensor_data
+    gpu.raw("h3_flash_bf16", data(ty), data(tq), data(tk), data(tv), None, 1, Lc, Hq, KH, SCALE, causal,
+            gpu.lib.h3b_gpu_stream(gpu.gpu))
+    want, _ = oracle.attention(q, k, v, SCALE, causal=causal)
+    assert_attention_close(oracle.from_bf16(gpu.read(ty, q.shape)), want)
+    for t in (ty, tq, tk, tv):
+        gpu.free(t)
+    # segmented keys
+    n = int(rng.integers(1, 7))
+    ranges = [near() for _ in range(n)]
+    nq = near()
+    q = oracle.normal_bf16((nq, H, 128), 3700 + seed)
+    ks = [oracle.normal_bf16((r, H, 128), 3800 + 10 * seed + i) for i, r in enumerate(ranges)]
+    vs = [oracle.normal_bf16((r, H, 128), 3900 + 10 * seed + i) for i, r in enumerate(ranges)]
+    tensors = [gpu.tensor(x) for x in ks + vs]
+    tk = (C.c_void_p * n)(*tensors[:n])
+    tv = (C.c_void_p * n)(*tensors[n:])
+    rows = (C.c_uint32 * n)(*ranges)
+    offs = (C.c_size_t * n)(*([0] * n))
+    tq, out = gpu.tensor(q), gpu.tensor(np.zeros((nq, H, 128), dtype=np.uint16))
+    assert gpu.lib.h3b_cross_attention_segments_bf16(gpu.gpu, out, 0, tq, 0, nq, H, n, tk, tv, offs, rows), gpu.error()
+    want, _ = oracle.attention(q[None], np.concatenate(ks)[None], np.concatenate(vs)[None], SCALE)
+    assert_attention_close(oracle.from_bf16(gpu.read(out, (nq, H, 128))), want[0])
+    for t in tensors + [tq, out]:
+        gpu.free(t)
+    assert gpu.device_status() == 0
