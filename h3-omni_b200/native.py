@@ -42,10 +42,24 @@ def _ctype(text, is_argument):
     return _CTYPES[base]
 
 
+def _preload_bundled_nccl():
+    """One NCCL per process: when a Python-packaged NCCL is installed (the one torch is built
+    against), load it first so that this library binds to it whether torch is imported before or
+    after; with the system NCCL loaded first, a later `import torch` fails to resolve symbols."""
+    import importlib.util
+    spec = importlib.util.find_spec("nvidia.nccl")
+    for root in (spec.submodule_search_locations if spec else []):
+        path = Path(root) / "lib" / "libnccl.so.2"
+        if path.exists():
+            C.CDLL(str(path), mode=C.RTLD_GLOBAL)
+            return
+
+
 def load_library():
     """Load the shared library and type every declared function. Raises if it is missing."""
     if not LIB.exists():
         raise RuntimeError("libh3b200_attn.so is not built; run `python h3-omni_b200/build.py`")
+    _preload_bundled_nccl()
     lib = C.CDLL(str(LIB))
     for result, name, args in declarations():
         fn = getattr(lib, name)
