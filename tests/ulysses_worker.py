@@ -141,6 +141,55 @@ def main():
     for t in slots:
         lib.h3_gpu_tensor_free(t)
     lib.h3b_exchange_free(x)
+
+    # ---- video sparse attention under Ulysses (reference h3_dit.c:2496-2525: scatter q, k, v and
+    # the gate, VSA on this rank's heads over the whole sequence, gather): bit-identical to the
+    # same call with all heads on one GPU ----
+    text, audio, grid = 21, 64, (4, 8, 16)
+    Lv = text + audio + grid[0] * grid[1] * grid[2]
+    vplan = ulysses.plan(Lv, H, world)
+    vrows = vplan.shard_rows
+    vfull = [oracle.normal_bf16((vplan.padded_rows, H, D), 900 + i, 0.3 if i == 3 else 1.0) for i in range(4)]
+    for t in vfull:
+        t[Lv:] = 0
+    x2, handle2 = C.c_void_p(), (C.c_ubyte * 64)()
+    assert lib.h3b_exchange_create(gpu.gpu, rank, world, vrows * H * D, 5, C.byref(x2), handle2), gpu.error()
+    tmp = rdv / ("ipcv_%d.tmp" % rank)
+    tmp.write_bytes(bytes(handle2))
+    tmp.rename(rdv / ("ipcv_%d" % rank))
+    deadline = time.time() + 120
+    while not all((rdv / ("ipcv_%d" % r)).exists() for r in range(world)):
+        if time.time() > deadline:
+            raise SystemExit("handle rendezvous timed out")
+        time.sleep(0.05)
+    assert lib.h3b_exchange_connect(x2, b"".join((rdv / ("ipcv_%d" % r)).read_bytes() for r in range(world))), \
+        gpu.error()
+    vslots = [lib.h3b_exchange_slot(x2, i) for i in range(5)]
+    for i, t in enumerate(vfull):
+        shard = gpu.tensor(t.reshape(world, vrows, H, D)[rank])
+        assert lib.h3b_exchange_scatter_heads_bf16(x2, i, shard, vrows, H, D), gpu.error()
+    local_vsa = gpu.call("vsa_new", text, audio, *grid, H // world)
+    local_out = gpu.empty_bf16(world * vrows * (H // world) * D)
+    gpu.call("zero", local_out)
+    assert lib.h3_gpu_vsa_bf16(local_vsa, local_out, *vslots[:4]), gpu.error()
+    assert lib.h3b_exchange_gather_heads_bf16(x2, 4, local_out, vrows, H, D), gpu.error()
+    sharded = gpu.read(vslots[4], (vrows, H, D))
+    whole_vsa = gpu.call("vsa_new", text, audio, *grid, H)
+    whole_out = gpu.empty_bf16(Lv * H * D)
+    assert lib.h3_gpu_vsa_bf16(whole_vsa, whole_out, *[gpu.tensor(t[:Lv]) for t in vfull]), gpu.error()
+    whole = gpu.read(whole_out, (Lv, H, D))
+    lo, hi = rank * vrows, min(Lv, (rank + 1) * vrows)
+    assert np.array_equal(sharded[:hi - lo], whole[lo:hi]), "VSA over head shards differs from one GPU"
+    stages = oracle.vsa_forward(*[t[:Lv] for t in vfull], oracle.VsaMap(text, audio, *grid))
+    want = oracle.from_bf16(stages["out"][lo:hi]).astype(np.float64)
+    got = oracle.from_bf16(sharded[:hi - lo]).astype(np.float64)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) < 0.012   # reference tests/fasth3/vsa.py:131
+    assert gpu.device_status() == 0
+    lib.h3_gpu_vsa_free(local_vsa)
+    lib.h3_gpu_vsa_free(whole_vsa)
+    for t in vslots:
+        lib.h3_gpu_tensor_free(t)
+    lib.h3b_exchange_free(x2)
     lib.h3_gpu_comm_free(comm)
     gpu.close()
     print("OK rank %d" % rank, flush=True)
