@@ -390,6 +390,9 @@ def main():
     if not args.no_also and not args.sequence:
         dit = dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_over_ranks,
                        exchange=exchange, slots=slots)
+    vsa_sharded = None
+    if not args.no_also and not args.sequence and world > 1 and exchange is not None:
+        vsa_sharded = vsa_step_sharded(gpu, torch, dist, device, stream, world, rank, barrier, max_over_ranks)
     if rank == 0 and world == 1:
         oracle = entry.load_oracle()
         oracle.build()
@@ -400,6 +403,8 @@ def main():
             line["also"] = secondary(gpu, torch, device, stream, pk)
     if dit is not None:
         line.setdefault("also", {})["dit_step"] = dit
+    if vsa_sharded is not None:
+        line.setdefault("also", {})["vsa_step"] = vsa_sharded
     if rank == 0:
         print(json.dumps(line), flush=True)
     if exchange is not None:
@@ -494,6 +499,71 @@ def dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_o
                         "exchanges from this library; GEMMs and other elementwise ops torch" % (plan.sequence, HEADS, hidden, ffn),
             "ms_per_step": ms, "n_gpus": world, "steps": steps, "blocks": blocks,
             "model_tflops": (gemm_flops + attn_flops) / ms / 1e9}
+
+
+def vsa_step_sharded(gpu, torch, dist, device, stream, world, rank, barrier, max_over_ranks, steps=5):
+    """Video sparse attention at N GPUs (reference h3_dit.c:2496-2546): this rank's rows of q, k, v
+    and the gate are scattered to head shards with the fused exchange, VSA runs on heads/N heads
+    over the whole sequence, the output is gathered back to row shards."""
+    from h3_omni_b200 import ulysses
+    lib = gpu.lib
+    text, audio, grid = 64, 512, (32, 30, 54)
+    sequence = text + audio + grid[0] * grid[1] * grid[2]
+    plan = ulysses.plan(sequence, HEADS, world)
+    rows, hg = plan.shard_rows, plan.local_heads
+    g = torch.Generator(device=device)
+    g.manual_seed(1003 * 1000 + rank)
+    shard = [torch.randn(rows, HEADS, DIM, generator=g, device=device).to(torch.bfloat16) for _ in range(3)]
+    shard.append((0.3 * torch.randn(rows, HEADS, DIM, generator=g, device=device)).to(torch.bfloat16))
+    for t in shard:
+        t[plan.valid_rows(rank):] = 0
+    xh, handle = C.c_void_p(), (C.c_ubyte * 64)()
+    if not lib.h3b_exchange_create(gpu.gpu, rank, world, rows * HEADS * DIM, 5, C.byref(xh), handle):
+        raise RuntimeError(gpu.error())
+    mine = torch.tensor(list(handle), dtype=torch.uint8, device=device)
+    everyone = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(everyone, mine)
+    if not lib.h3b_exchange_connect(xh, bytes(torch.cat(everyone).cpu().tolist())):
+        raise RuntimeError(gpu.error())
+    slots = [C.c_void_p(lib.h3b_exchange_slot(xh, i)) for i in range(5)]
+    vsa = gpu.call("vsa_new", text, audio, *grid, hg)
+    info = [C.c_int() for _ in range(4)]
+    lib.h3b_vsa_info(vsa, *[C.byref(x) for x in info])
+    tiles, prefix = info[1].value, info[2].value
+    lib.h3b_vsa_set_keep(vsa, (tiles - prefix) // 8)
+    local_out = torch.zeros(world * rows, hg, DIM, device=device, dtype=torch.bfloat16)
+    tshard = [gpu.wrap(t.data_ptr(), t.numel()) for t in shard]
+    tout = gpu.wrap(local_out.data_ptr(), local_out.numel())
+    dist.barrier()
+
+    def step():
+        for i, t in enumerate(tshard):
+            if not lib.h3b_exchange_scatter_heads_bf16(xh, i, t, rows, HEADS, DIM):
+                raise RuntimeError(gpu.error())
+        if not lib.h3_gpu_vsa_bf16(vsa, tout, slots[0], slots[1], slots[2], slots[3]):
+            raise RuntimeError(gpu.error())
+        if not lib.h3b_exchange_gather_heads_bf16(xh, 4, tout, rows, HEADS, DIM):
+            raise RuntimeError(gpu.error())
+
+    for _ in range(2):
+        step()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(steps):
+        step()
+    b.record(stream)
+    barrier()
+    ms = max_over_ranks(a.elapsed_time(b) / steps)
+    torch.cuda.synchronize()
+    dist.barrier()
+    lib.h3_gpu_vsa_free(vsa)
+    for t in slots:
+        lib.h3_gpu_tensor_free(t)
+    lib.h3b_exchange_free(xh)
+    return {"workload": "video sparse attention step at %d GPUs: 4 fused scatters, VSA on %d heads over %d rows "
+                        "(%d tiles, keep 12.5 %%), fused gather" % (world, hg, sequence, tiles),
+            "ms_per_step": ms, "n_gpus": world, "steps": steps}
 
 
 def secondary(gpu, torch, device, stream, pk, only=None, steps=5):
