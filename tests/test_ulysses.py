@@ -116,3 +116,54 @@ def test_multi_rank_scatter_attention_gather(gpu):
             outputs.append(out)
         for r, (p, out) in enumerate(zip(procs, outputs)):
             assert p.returncode == 0 and "OK rank %d" % r in out, out[-2000:]
+
+
+@pytest.mark.gpu
+def test_one_process_thread_per_device(gpu, oracle):
+    """The reference's own arrangement (h3_dit.c:4031-4185): one process, h3_gpu_comm_init_all,
+    one host thread and one h3_gpu context per device. Scatter and gather of a row shard per
+    thread against the oracle's index algebra. Run in a child process (its CUDA contexts on
+    several devices should not outlive the test); skipped on a single-GPU box."""
+    if gpu.lib.h3_gpu_device_count() < 2:
+        pytest.skip("needs 2 or more GPUs")
+    code = r'''
+import ctypes as C, sys, threading
+import numpy as np
+sys.path.insert(0, %r)
+import __graft_entry__ as entry
+entry.load_package()
+from h3_omni_b200 import native
+oracle = entry.load_oracle()
+lib = native.load_library()
+world, rows, H, D = 2, 77, 6, 128
+comms = (C.c_void_p * world)()
+err = C.create_string_buffer(256)
+assert lib.h3_gpu_comm_init_all(world, comms, err, 256), err.value
+shards = oracle.normal_bf16((world, rows, H, D), 41)
+want = oracle.ulysses(shards)
+failures = []
+def run(rank):
+    try:
+        assert lib.h3_gpu_select_device(rank, err, 256), err.value
+        g = native.Native()
+        comm = C.c_void_p(comms[rank])
+        assert lib.h3b_comm_rank(comm) == rank and lib.h3b_comm_size(comm) == world
+        t, scratch = g.tensor(shards[rank]), g.empty_bf16(rows * H * D)
+        g.call("ulysses_scatter_heads_bf16", comm, t, scratch, rows, H, D)
+        assert np.array_equal(g.read(t, (world * rows, H // world, D)), want[rank]), "scatter"
+        g.call("ulysses_gather_heads_bf16", comm, t, scratch, rows, H, D)
+        assert np.array_equal(g.read(t, (rows, H, D)), shards[rank]), "gather"
+        assert g.device_status() == 0
+        g.close()
+    except BaseException as e:   # reported by the main thread
+        failures.append("rank %%d: %%r" %% (rank, e))
+threads = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+for t in threads: t.start()
+for t in threads: t.join(120)
+assert not failures and not any(t.is_alive() for t in threads), failures
+for r in range(world): lib.h3_gpu_comm_free(C.c_void_p(comms[r]))
+print("OK threads")
+''' % str(ROOT)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, env=env)
+    assert p.returncode == 0 and "OK threads" in p.stdout, (p.stdout + p.stderr)[-3000:]
