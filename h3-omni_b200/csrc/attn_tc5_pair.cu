@@ -213,13 +213,11 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     if (!wait_stage(2 * j + 2)) break;
                     TRACE_ADD(2);
                 }
-#ifndef H3B_EXP_NO_PWAIT
                 {
                     TRACE_T0();
                     if (!mbar_wait(bar_p_full(0), j & 1, &abort_word)) break;
                     TRACE_ADD(0);
                 }
-#endif
                 tc5_fence_after();
                 {
                     TRACE_T0();
@@ -231,13 +229,11 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     issue_qk(j + 1, 0);
                     TRACE_ADD(5);
                 }
-#ifndef H3B_EXP_NO_PWAIT
                 {
                     TRACE_T0();
                     if (!mbar_wait(bar_p_full(1), j & 1, &abort_word)) break;
                     TRACE_ADD(3);
                 }
-#endif
                 tc5_fence_after();
                 issue_pv(j, 1);
                 mma_commit(bar_empty((2 * j + 1) % ST));
@@ -293,10 +289,6 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const long long trace_work = clock64();
 #endif
             bool saw_prev_pv = (j == 0);
-#ifdef H3B_SKIP_SOFTMAX
-            if (true) {   // experiment: no softmax work at all, P = whatever S holds
-            } else
-#endif
             if (nvalid >= PBN) {
                 // the whole row of scores in registers: one TMEM read pass
                 uint32_t s0[32], s1[32], s2[32], s3[32];
