@@ -167,3 +167,29 @@ print("OK threads")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, env=env)
     assert p.returncode == 0 and "OK threads" in p.stdout, (p.stdout + p.stderr)[-3000:]
+
+
+@pytest.mark.gpu
+def test_full_size_ten_second_clip_over_ranks(gpu):
+    """Benchmark config 4 (L = 101,464, H = 24) over 2 GPUs (4 when the box has them): fused scatters,
+    attention with fused gather, sampled rows against the FP64 recomputation. One child process
+    per GPU; skipped on a single-GPU box."""
+    count = gpu.lib.h3_gpu_device_count()
+    if count < 2:
+        pytest.skip("needs 2 or more GPUs")
+    world = 4 if count >= 4 else 2
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    with tempfile.TemporaryDirectory() as rdv:
+        procs = [subprocess.Popen([sys.executable, str(ROOT / "tests" / "c4_worker.py"), str(r), str(world), rdv],
+                                  stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
+                 for r in range(world)]
+        outputs = []
+        for p in procs:
+            try:
+                out, _ = p.communicate(timeout=900)
+            except subprocess.TimeoutExpired:
+                p.kill()
+                out, _ = p.communicate()
+            outputs.append(out)
+        for r, (p, out) in enumerate(zip(procs, outputs)):
+            assert p.returncode == 0 and "OK rank %d" % r in out, out[-2000:]
