@@ -1,7 +1,7 @@
 """One rank of the full-size Ulysses parity check (benchmark config: 10 s clip, L = 62*1620 + 1024 =
 101,464 rows, H = 24, sequence sharded by rank).
 
-usage: c4_worker.py RANK WORLD RENDEZVOUS_DIR
+usage: long_clip_worker.py RANK WORLD RENDEZVOUS_DIR
 Every rank generates the seeded full tensors, keeps its row shard on the GPU, runs the three fused
 head scatters and the attention with the gather fused into its epilogue, and checks sampled rows
 of its own output shard against the FP64 recomputation of the reference's microbenchmark

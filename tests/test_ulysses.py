@@ -180,7 +180,7 @@ def test_full_size_ten_second_clip_over_ranks(gpu):
     world = 4 if count >= 4 else 2
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     with tempfile.TemporaryDirectory() as rdv:
-        procs = [subprocess.Popen([sys.executable, str(ROOT / "tests" / "c4_worker.py"), str(r), str(world), rdv],
+        procs = [subprocess.Popen([sys.executable, str(ROOT / "tests" / "long_clip_worker.py"), str(r), str(world), rdv],
                                   stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)
                  for r in range(world)]
         outputs = []
