@@ -41,6 +41,18 @@ cudaError_t attn_sparse_tc5(void *out, const void *q, const void *k, const void 
                             const int *indices, const int *counts, const int *sizes,
                             unsigned tiles, unsigned heads, cudaStream_t stream);
 
+// The persistent block-sparse kernel with the keys on the MMA's M axis (attn_sparse_t.cu). mq has
+// a 64-row box; `ticket` (one zeroed word) and `redo` ([heads][tiles] bytes) are work memory the
+// caller provides on `stream`; tiles whose row sums left the safe exponent range are marked in redo.
+cudaError_t attn_sparse_t_launch(const ::CUtensorMap_st *mq, const ::CUtensorMap_st *mk,
+                                 const ::CUtensorMap_st *mv, void *out, float *lse, const int *indices,
+                                 const int *counts, const int *sizes, unsigned tiles, unsigned heads,
+                                 unsigned *ticket, unsigned char *redo, bool force_redo, int *status,
+                                 cudaStream_t stream);
+// 0: persistent kernel, marked tiles recomputed by the pair-walk kernel (default); 1: pair-walk
+// kernel only; 2: persistent kernel with every tile marked (exercises the recomputation).
+void attn_sparse_set_mode(int mode);
+
 // Warp-level mma.sync kernel (attn_mma.cu): causal / GQA bf16 D=128 and fp16 D=64.
 // elem: 0 = bf16 (dim 128), 1 = fp16 (dim 64).
 cudaError_t attn_mma(void *out, const void *q, const void *k, const void *v, float *lse,

@@ -43,6 +43,7 @@ struct Tc5Params {
     __nv_bfloat16 *out;
     float *lse;
     const int *indices, *counts, *sizes;
+    const unsigned char *redo;   // sparse: when set, only query tiles marked here are computed
     int tiles;
     int *status;
 };
@@ -91,6 +92,13 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int kv_head = SPARSE ? head : head / (p.heads / p.kv_heads);
     const int q_row0 = blockIdx.x * BM;  // dense: token row; sparse: padded tiled row
 
+    if (SPARSE && p.redo) {
+        // recomputation pass: leave at once unless one of this CTA's two query tiles is marked
+        const size_t first = (size_t)head * p.tiles + blockIdx.x * 2;
+        const bool second = blockIdx.x * 2 + 1 < p.tiles;
+        if (!p.redo[first] && !(second && p.redo[first + 1])) return;
+    }
+
     if (tid == 0) {
         mbar_init(bar_q_full(), 1);
         for (int s = 0; s < ST; s++) {
@@ -126,8 +134,12 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // Bitmaps of the KV tiles selected by query tile A (rows 0-63) and B (rows 64-127).
         const int qa = blockIdx.x * 2, qb = qa + 1;
         const size_t row_a = (size_t)head * p.tiles + qa;
-        const int count_a = min(p.counts[row_a], p.tiles);
-        const int count_b = qb < p.tiles ? min(p.counts[row_a + 1], p.tiles) : 0;
+        const int raw_a = p.counts[row_a], raw_b = qb < p.tiles ? p.counts[row_a + 1] : 0;
+        // a count outside [0, tiles] is refused like a bad index; the list is clamped
+        if (tid == 0 && (raw_a < 0 || raw_a > p.tiles || raw_b < 0 || raw_b > p.tiles))
+            atomicCAS(p.status, STATUS_OK, STATUS_BAD_ARGUMENT);
+        const int count_a = max(0, min(raw_a, p.tiles));
+        const int count_b = max(0, min(raw_b, p.tiles));
         for (int i = tid; i < count_a + count_b; i += TC5_THREADS) {
             const bool is_a = i < count_a;
             const int kt = is_a ? p.indices[row_a * p.tiles + i]
@@ -347,9 +359,19 @@ attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             alive = __all_sync(0xffffffffu,
                                mbar_wait(bar_pv_done, (n_tiles - 1) & 1, &abort_word));
         }
+        if (SPARSE && alive && n_tiles == 0) {
+            // neither query tile selected anything: defined result, zero rows
+            const int padded = q_row0 + r;
+            if (padded < p.tiles * 64) {
+                uint4 *d4 = reinterpret_cast<uint4 *>(p.out + ((size_t)head * p.tiles * 64 + padded) * HD);
+#pragma unroll
+                for (int i = 0; i < HD / 8; i++) d4[i] = make_uint4(0u, 0u, 0u, 0u);
+                if (p.lse) p.lse[(size_t)head * p.tiles * 64 + padded] = INFINITY;
+            }
+        }
         if (alive && n_tiles > 0) {
             tc5_fence_after();
-            const float inv = 1.0f / l;
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;   // a half with an empty list: zero rows
             bool store;
             __nv_bfloat16 *dst;
             if (SPARSE) {
@@ -527,6 +549,11 @@ cudaError_t attn_segments_tc5(void *out, const void *q, const void *const *k, co
                                nullptr, segments, segment_rows);
 }
 
+namespace {
+int g_sparse_mode = 0;
+}
+void attn_sparse_set_mode(int mode) { g_sparse_mode = mode; }
+
 cudaError_t attn_sparse_tc5(void *out, const void *q, const void *k, const void *v, float *lse,
                             const int *indices, const int *counts, const int *sizes,
                             unsigned tiles, unsigned heads, cudaStream_t stream) {
@@ -534,11 +561,12 @@ cudaError_t attn_sparse_tc5(void *out, const void *q, const void *k, const void 
     int *status = nullptr;
     cudaError_t e = device_status_word(&status);
     if (e != cudaSuccess) return e;
-    CUtensorMap mq, mk, mv;
+    CUtensorMap mq, mq64, mk, mv;
     const uint64_t dims[4] = {128, (uint64_t)tiles * 64, heads, 1};
     const uint64_t strides[3] = {256, (uint64_t)tiles * 64 * 256, (uint64_t)heads * tiles * 64 * 256};
     const uint32_t box_q[4] = {64, 128, 1, 1}, box_kv[4] = {64, 64, 1, 1};
     if ((e = make_map(&mq, q, dims, strides, box_q)) != cudaSuccess) return e;
+    if ((e = make_map(&mq64, q, dims, strides, box_kv)) != cudaSuccess) return e;
     if ((e = make_map(&mk, k, dims, strides, box_kv)) != cudaSuccess) return e;
     if ((e = make_map(&mv, v, dims, strides, box_kv)) != cudaSuccess) return e;
     Tc5Params p{};
@@ -553,7 +581,25 @@ cudaError_t attn_sparse_tc5(void *out, const void *q, const void *k, const void 
     p.tiles = (int)tiles;
     p.status = status;
     dim3 grid((tiles + 1) / 2, heads, 1);
-    return launch<64, true>(mq, mk, mv, p, grid, stream);
+    const int mode = g_sparse_mode;
+    if (mode == 1) return launch<64, true>(mq, mk, mv, p, grid, stream);
+    // Work memory of the persistent kernel, stream-ordered like the logsumexp buffer the
+    // reference's wrapper allocates per call (cuda/h3_gpu_cuda.cu:1115-1127): one ticket word
+    // and one mark per query tile.
+    unsigned char *work = nullptr;
+    const size_t work_bytes = 256 + (size_t)tiles * heads;
+    if ((e = cudaMallocAsync(reinterpret_cast<void **>(&work), work_bytes, stream)) != cudaSuccess) return e;
+    e = cudaMemsetAsync(work, 0, 256, stream);
+    if (e == cudaSuccess)
+        e = attn_sparse_t_launch(&mq64, &mk, &mv, out, lse, indices, counts, sizes, tiles, heads,
+                                 reinterpret_cast<unsigned *>(work), work + 256, mode == 2, status, stream);
+    if (e == cudaSuccess) {
+        // marked tiles (row sums outside the safe exponent range) are recomputed with per-row maxima
+        p.redo = work + 256;
+        e = launch<64, true>(mq, mk, mv, p, grid, stream);
+    }
+    const cudaError_t freed = cudaFreeAsync(work, stream);
+    return e != cudaSuccess ? e : freed;
 }
 
 }  // namespace h3b

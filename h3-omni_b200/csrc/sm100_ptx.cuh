@@ -84,6 +84,39 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     return __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
 }
 
+// The same with the loop run by the whole warp and only the probe predicated on lane 0: no
+// divergent loop, so the registers of a register-heavy caller stay where they are.
+__device__ __forceinline__ bool mbar_wait_uniform(uint32_t bar, uint32_t parity, volatile int *abort_word) {
+    const bool prober = (threadIdx.x & 31) == 0;
+    unsigned long long start = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t done = 0;
+        if (prober) done = mbar_try_wait(bar, parity) ? 1u : 0u;
+        if (__shfl_sync(0xffffffffu, done, 0)) return true;
+        if ((spin & 255u) == 255u) {
+            uint32_t stop = 0;
+            if (prober) {
+                const unsigned long long now = global_timer_ns();
+                if (!start) start = now;
+                if (*abort_word) stop = 1;
+                else if (now - start > WAIT_LIMIT_NS) {
+                    *abort_word = 1;
+                    stop = 1;
+                }
+            }
+            if (__shfl_sync(0xffffffffu, stop, 0)) return false;
+        }
+    }
+}
+
+// Lane 0 polls, the other lanes wait for it at a warp barrier; the outcome travels through the
+// abort word (a wait only fails by raising it), so no shuffle is needed.
+__device__ __forceinline__ bool mbar_wait_lane0(uint32_t bar, uint32_t parity, volatile int *abort_word) {
+    if ((threadIdx.x & 31) == 0) mbar_wait(bar, parity, abort_word);
+    __syncwarp();
+    return *abort_word == 0;
+}
+
 // ---- TMA (non-multicast tile loads only) ---------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");

@@ -288,6 +288,13 @@ int h3b_vsa_qkv_rope_bf16(h3_gpu_vsa *vsa, h3_gpu_tensor *output, const h3_gpu_t
                           const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
                           const h3_gpu_tensor *gate, uint32_t rope_half, float epsilon, int grouped);
 
+/* Which kernel runs the block-sparse fine stage behind h3_vsa_hopper (process-wide; for A/B
+ * measurement and tests). 0 (default): the persistent kernel that walks each query tile's own
+ * list, with the rare tiles whose softmax sums leave the safe exponent range recomputed by the
+ * pair-walk kernel; 1: the pair-walk kernel only (two adjacent query tiles per CTA walk the
+ * union of their lists, per-row online softmax); 2: as 0 with every tile recomputed. */
+void h3b_vsa_fine_mode(int mode);
+
 /* Top-k tile selection of video sparse attention with no device allocation at all. It has no
  * counterpart in the reference: it is for callers that cannot allocate where they call from -
  * a host that gave this code a fixed memory arena at start-up, a memory-capped deployment
