@@ -90,17 +90,31 @@ cudaError_t qkv_rope_head_shards(const QkvRopeInput &in, void *const window_q[],
 cudaError_t qkv_rope_vsa_tiles(const QkvRopeInput &in, const int *map, const int *sizes, int tiles,
                                void *const tiled[3], float *const pooled[3], cudaStream_t stream);
 
-// Ulysses local transposes (ulysses.cu): out[b][a][c] = in[a][b][c], c in 16-byte units.
-cudaError_t swap_leading_16b(void *out, const void *in, unsigned a, unsigned b, size_t c_units,
-                             cudaStream_t stream);
+// Ulysses block transpose (ulysses.cu): out[b][a][:] = in[a][b][:], rows of `row_units` 16-byte units.
+cudaError_t transpose_rows_16b(void *out, const void *in, unsigned a, unsigned b, size_t row_units,
+                               cudaStream_t stream);
 
-// Fused transpose + all-to-all over peer memory (ulysses.cu). window[p] / flags[p] are this
-// process's mappings of rank p's window slot and flag array.
-// Epoch handshake alone (after a kernel that stored into the peers' windows itself).
-cudaError_t exchange_handshake(unsigned long long *const flags[], unsigned long long epoch, int *status,
-                               int rank, int ranks, cudaStream_t stream);
-cudaError_t exchange_push(bool gather, const void *src, void *const window[], unsigned long long *const flags[],
-                          unsigned long long epoch, unsigned *done_counter, int *status, int rank, int ranks,
-                          unsigned rows, unsigned heads, unsigned dim, cudaStream_t stream);
+// Fused exchange over peer memory (ulysses.cu). Every rank's window ends in one flag block.
+constexpr int EXCHANGE_MAX_RANKS = 16, EXCHANGE_MAX_TENSORS = 4;
+struct ExchangeFlags {
+    unsigned long long done[EXCHANGE_MAX_RANKS];    // done[p]: last exchange whose data from rank p is complete here
+    unsigned long long ready[EXCHANGE_MAX_RANKS];   // ready[p]: last exchange rank p has started
+    unsigned counter;                               // CTAs of the running push kernel that have finished
+    unsigned reserved[63];
+};
+struct ExchangeSync {
+    ExchangeFlags *flags[EXCHANGE_MAX_RANKS];   // this process's mappings of every rank's flag block
+    unsigned long long epoch;                   // number of this exchange, the same on every rank
+    unsigned long long limit_ns;                // bound of every flag wait
+    int *status;                                // device status word of this rank
+    int rank, ranks;
+};
+// `tensors` (<= 4) tensors in one launch: src[t] goes to window[t][p] on rank p.
+cudaError_t exchange_push(bool gather, int tensors, const void *const src[],
+                          void *const window[][EXCHANGE_MAX_RANKS], const ExchangeSync &sync, unsigned rows,
+                          unsigned heads, unsigned dim, cudaStream_t stream);
+// Open / close around a kernel that stores into the peers' windows itself.
+cudaError_t exchange_open(const ExchangeSync &sync, cudaStream_t stream);
+cudaError_t exchange_close(const ExchangeSync &sync, cudaStream_t stream);
 
 }  // namespace h3b

@@ -414,7 +414,8 @@ cudaError_t vsa_score_select_compress(const float *poolq, const float *poolk, co
                                       int heads, float scale, cudaStream_t stream) {
     if (tiles < 1 || tiles > 4096 || keep < 1 || prefix < 0 || prefix > tiles)
         return cudaErrorInvalidValue;
-    // 16 query tiles per CTA while two CTAs still fit an SM, 8 beyond that.
+    // 16 query tiles per CTA up to 1400 tiles (two such CTAs share an SM up to about 1130 tiles,
+    // one beyond), 8 per CTA beyond that: the score rows of a CTA must fit its shared memory.
     if (tiles <= 1400)
         return launch_score_select<2>(poolq, poolk, poolv, scores, indices, counts, compression, tiles,
                                       prefix, keep, heads, scale, stream);
@@ -479,18 +480,19 @@ extern "C" cudaError_t h3b_vsa_topk_static(const void *query, const void *key, c
     // Device address of the scratch array, resolved once per device with that device current.
     // (In host code the array's name is only a handle for the runtime, not an address.)
     static float *pool_of_device[64] = {};
+    // every failing return leaves its reason in the thread's error text
+    auto failed = [](cudaError_t code, const char *where) {
+        snprintf(g_topk_error, sizeof g_topk_error, "h3b_vsa_topk_static: %s: %s", where, cudaGetErrorString(code));
+        return code;
+    };
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
-    if (e != cudaSuccess) return e;
-    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    if (e != cudaSuccess) return failed(e, "current device");
+    if (device < 0 || device >= 64) return failed(cudaErrorInvalidDevice, "device ordinal above 63");
     float *pool = __atomic_load_n(&pool_of_device[device], __ATOMIC_ACQUIRE);
     if (!pool) {
         e = cudaGetSymbolAddress(reinterpret_cast<void **>(&pool), g_topk_pool);
-        if (e != cudaSuccess) {
-            snprintf(g_topk_error, sizeof g_topk_error, "h3b_vsa_topk_static: %s",
-                     cudaGetErrorString(e));
-            return e;
-        }
+        if (e != cudaSuccess) return failed(e, "address of the static scratch");
         __atomic_store_n(&pool_of_device[device], pool, __ATOMIC_RELEASE);
     }
     float *poolq = pool, *poolk = pool + (size_t)STATIC_TOPK_MAX_ROWS * VD;
@@ -498,8 +500,8 @@ extern "C" cudaError_t h3b_vsa_topk_static(const void *query, const void *key, c
     void *no_tiled[3] = {nullptr, nullptr, nullptr};
     float *pooled[3] = {poolq, poolk, nullptr};
     e = vsa_tile_pool3(src, no_tiled, pooled, map, sizes, (int)tiles, (int)heads, 2, stream);
-    if (e != cudaSuccess) return e;
-    return vsa_score_select_compress(poolq, poolk, nullptr, nullptr, indices, counts, nullptr,
-                                     (int)tiles, (int)prefix, (int)keep, (int)heads,
-                                     1.0f / sqrtf(128.0f), stream);
+    if (e != cudaSuccess) return failed(e, "pooling launch");
+    e = vsa_score_select_compress(poolq, poolk, nullptr, nullptr, indices, counts, nullptr, (int)tiles,
+                                  (int)prefix, (int)keep, (int)heads, 1.0f / sqrtf(128.0f), stream);
+    return e == cudaSuccess ? e : failed(e, "selection launch");
 }

@@ -178,7 +178,10 @@ int h3_gpu_all_gather_bf16(h3_gpu *gpu, h3_gpu_comm *comm, h3_gpu_tensor *output
 
 /* Device status word of the current device: 0 = ok, 1 = a bounded device-side wait gave
  * up, 2 = a device-side bounds check refused an access. Synchronises the device.
- * reset != 0 clears the word after reading. */
+ * reset != 0 clears the word after reading. h3_gpu_submit reports a non-zero word as a failure
+ * ("device-side wait timed out (status 1)" / "device-side bounds check failed (status 2)") once
+ * and clears it; the word belongs to the device, so a failure raised through one context is
+ * reported by whichever context of that device submits next. */
 cudaError_t h3b_device_status(int *status, int reset);
 
 /* Wrap device memory the caller owns (e.g. a framework tensor) as a non-owning
@@ -230,18 +233,48 @@ int h3b_comm_size(const h3_gpu_comm *comm);
  * status word, not a hang). The destination of both calls is slot `slot` of every rank's window:
  *   scatter: src [rows][heads][dim] per rank -> [ranks*rows][heads/ranks][dim] per rank
  *   gather : src [ranks*rows][heads/ranks][dim] per rank -> [rows][heads][dim] per rank
- * Calls must be made in the same order on every rank, on the context's stream; a slot must not
- * be overwritten before its readers on that rank were enqueued on the same stream. */
+ * Calls must be made in the same order on every rank, each on its context's stream. Reusing a slot
+ * is safe by construction: an exchange starts storing only after every rank has STARTED the same
+ * exchange, and a rank starts it only after everything queued before it on its stream - the
+ * readers of what earlier exchanges left in its window - has finished. So the one rule is: queue
+ * the readers of a slot on the exchange's stream before the next exchange call of any kind.
+ * After a timeout (status 1) nothing more is stored and the failure shows on every rank. */
 typedef struct h3b_exchange h3b_exchange;
 int h3b_exchange_create(h3_gpu *gpu, int rank, int ranks, size_t slot_elements, int slots,
                         h3b_exchange **exchange, void *handle64);
 int h3b_exchange_connect(h3b_exchange *exchange, const void *handles);
+/* The ranks as threads of ONE process (how the reference runs them, h3_dit.c:4066-4177): a CUDA IPC
+ * handle cannot be opened by the process that made it, so the windows are joined by their device
+ * pointers and peer access is switched on between the devices. all_ranks: every rank's exchange in
+ * rank order. Each rank calls this for its own exchange with its own device current, after all
+ * ranks have created theirs. */
+int h3b_exchange_connect_local(h3b_exchange *exchange, h3b_exchange *const *all_ranks);
+/* Bound of every device-side wait of this exchange's kernels, default 2000 ms. */
+int h3b_exchange_set_wait_limit_ms(h3b_exchange *exchange, unsigned milliseconds);
+const char *h3b_exchange_error(const h3b_exchange *exchange);
 void h3b_exchange_free(h3b_exchange *exchange);
 h3_gpu_tensor *h3b_exchange_slot(h3b_exchange *exchange, int slot);
 int h3b_exchange_scatter_heads_bf16(h3b_exchange *exchange, int slot, const h3_gpu_tensor *src,
                                     uint32_t rows, uint32_t heads, uint32_t dim);
 int h3b_exchange_gather_heads_bf16(h3b_exchange *exchange, int slot, const h3_gpu_tensor *src,
                                    uint32_t rows, uint32_t heads, uint32_t dim);
+/* Up to four tensors of one shape (q, k, v, and the gate of video sparse attention) scattered by
+ * ONE kernel with one pair of handshakes: sources[t] goes to slot slots[t]. Replaces the three or
+ * four exchanges per block of h3_dit.c:2529-2538. */
+int h3b_exchange_scatter_heads_multi_bf16(h3b_exchange *exchange, int count, const int *slots,
+                                          const h3_gpu_tensor *const *sources, uint32_t rows,
+                                          uint32_t heads, uint32_t dim);
+/* The same exchange for a backend that keeps its own tensor and context objects: no h3_gpu, raw
+ * device pointers, the stream given per call, cudaError_t results (text: h3b_exchange_error).
+ * handle64 may be NULL when the ranks will be joined with h3b_exchange_connect_local. */
+cudaError_t h3b_exchange_create_raw(int rank, int ranks, size_t slot_elements, int slots,
+                                    h3b_exchange **exchange, void *handle64);
+void *h3b_exchange_slot_pointer(h3b_exchange *exchange, int slot);
+cudaError_t h3b_exchange_scatter_raw(h3b_exchange *exchange, int count, const int *slots,
+                                     const void *const *sources, uint32_t rows, uint32_t heads,
+                                     uint32_t dim, cudaStream_t stream);
+cudaError_t h3b_exchange_gather_raw(h3b_exchange *exchange, int slot, const void *source, uint32_t rows,
+                                    uint32_t heads, uint32_t dim, cudaStream_t stream);
 
 /* Attention over this rank's heads/ranks heads with the sequence-gather fused into the kernel's
  * epilogue: q, k, v are [>= sequence][heads/ranks][128] (typically the scatter slots); each output
@@ -278,6 +311,31 @@ void *h3b_vsa_buffer(const h3_gpu_vsa *vsa, int which);
 int h3b_vsa_time_stages(h3_gpu_vsa *vsa, int enable);
 int h3b_vsa_stage_ms(h3_gpu_vsa *vsa, float *ms4);
 
+/* The stages of h3_gpu_vsa_bf16 on raw device pointers, for a backend that keeps its own tensor
+ * objects and adopts the stages one by one (they replace, in this order, the three tile_pool
+ * launches of cuda/vsa.cuh:274-278; the score SGEMM, select_blocks, pooled_softmax and the
+ * compression SGEMM of :281-294; untile_merge of :295-299; the block-sparse kernel between them is
+ * h3_vsa_hopper). source / tiled / pooled hold q, k, v in this order; layouts as in the reference:
+ * source and gate and output token-major [rows][heads][128] bf16, tiled [heads][tiles*64][128]
+ * bf16, pooled and compression [heads][tiles][128] f32, indices [heads][tiles][tiles], counts
+ * [heads][tiles], map [tiles*64], sizes [tiles] int32. scores ([heads][tiles][tiles] f32) may be
+ * NULL: the score matrix is then never written. compression may be NULL (selection only). */
+cudaError_t h3b_vsa_pool_raw(const void *const source[3], void *const tiled[3], float *const pooled[3],
+                             const int *map, const int *sizes, unsigned tiles, unsigned heads,
+                             cudaStream_t stream);
+cudaError_t h3b_vsa_select_raw(const float *pooled_q, const float *pooled_k, const float *pooled_v,
+                               float *scores, int *indices, int *counts, float *compression,
+                               unsigned tiles, unsigned prefix, unsigned keep, unsigned heads,
+                               cudaStream_t stream);
+cudaError_t h3b_vsa_merge_raw(void *output, const void *tiled_sparse, const void *gate,
+                              const float *compression, const int *map, unsigned tiles, unsigned heads,
+                              cudaStream_t stream);
+/* Q/K norm + RoPE on raw pointers (the arithmetic of h3_gpu_qkv_rope_bf16 / _grouped_). */
+cudaError_t h3b_qkv_rope_raw(void *query, void *key, void *value, const void *qkv, const void *q_norm,
+                             const void *k_norm, const void *rope_cos, const void *rope_sin,
+                             unsigned sequence, unsigned heads, unsigned rope_half, float epsilon,
+                             int grouped, cudaStream_t stream);
+
 /* Video sparse attention fed by the QKV projection output instead of separate q, k, v
  * (no counterpart in the reference, which runs h3_gpu_grouped_qkv_rope_bf16 and then
  * h3_gpu_vsa_bf16): norm + rotation write q, k, v directly in tile order together with the
@@ -306,7 +364,8 @@ void h3b_vsa_fine_mode(int mode);
  *   - Limit: heads * tiles <= 8192; larger shapes return cudaErrorInvalidValue and
  *     h3b_vsa_topk_static_error() says why. Nothing is launched in that case.
  *   - query, key: [rows][heads][128] bf16; map [tiles*64] and sizes [tiles] as built by
- *     h3_gpu_vsa_new (device pointers); indices and counts are written in full.
+ *     h3_gpu_vsa_new (device pointers). counts is written in full; of each indices row the
+ *     first counts[row] entries are written, the entries behind them keep the caller's bytes.
  *   - The first call on each device resolves the array's device address (a runtime query,
  *     no allocation); make that first call before starting any stream capture.
  *   - All calls share the one array and it keeps the previous call's contents. Every call

@@ -42,6 +42,16 @@ def test_sdpa_bf16_larger(gpu, oracle, L, H):
     assert gpu.device_status() == 0
 
 
+def test_c1_dense_l4096_h8(gpu, oracle):
+    """Benchmark configuration 1 exactly: Q, K, V bf16 [1, 8, 4096, 128] from N(0, 1), seed 1001,
+    scale 1/sqrt(128), no mask; max-abs <= 1e-2 and cosine >= 0.9999 against the FP32
+    recomputation (the whole output, every row)."""
+    got, want = run_sdpa(gpu, oracle, 4096, 8, 1001)
+    m = assert_attention_close(got, want)
+    assert m["rel_l2"] <= 0.004   # the level the reference's own kernel is held to on live shapes
+    assert gpu.device_status() == 0
+
+
 def test_sdpa_fa2_entry_matches_flash3_entry(gpu, oracle):
     """h3_gpu_sdpa_fa2_bf16 (FlashAttention-2 adapter path) and h3_gpu_sdpa_bf16 agree."""
     a, want = run_sdpa(gpu, oracle, 263, 4, 5, "sdpa_bf16")

@@ -28,7 +28,7 @@ def test_plan_matches_reference_sharding(package):
 
 
 def _gloo_rank(rank, world, port, rows, heads, dim, result):
-    """swap_leading + all_to_all exactly as the library orders them, on gloo."""
+    """Block transpose + all-to-all exactly as the library orders them, on gloo."""
     import torch
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -167,6 +167,70 @@ print("OK threads")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, env=env)
     assert p.returncode == 0 and "OK threads" in p.stdout, (p.stdout + p.stderr)[-3000:]
+
+
+@pytest.mark.gpu
+def test_fused_exchange_between_threads_of_one_process(gpu, oracle):
+    """The fused exchange in the reference's own arrangement - one process, one host thread and
+    one context per device: windows joined with h3b_exchange_connect_local (a CUDA IPC handle
+    cannot be opened by the process that made it). Scatter of q, k, v in one kernel, attention with
+    the gather fused into its epilogue, against the oracle. Child process; needs 2 GPUs."""
+    if gpu.lib.h3_gpu_device_count() < 2:
+        pytest.skip("needs 2 or more GPUs")
+    code = r'''
+import ctypes as C, sys, threading
+import numpy as np
+sys.path.insert(0, %r)
+import __graft_entry__ as entry
+entry.load_package()
+from h3_omni_b200 import native, ulysses
+oracle = entry.load_oracle()
+lib = native.load_library()
+world, H, D = 2, 4, 128
+L = 2 * 211 + 1
+plan = ulysses.plan(L, H, world)
+rows = plan.shard_rows
+scale = float(1 / np.sqrt(128.0))
+full = [oracle.normal_bf16((plan.padded_rows, H, D), 500 + i) for i in range(3)]
+for x in full: x[L:] = 0
+want, _ = oracle.attention(*[x[None, :L] for x in full], scale)
+err = C.create_string_buffer(256)
+exchanges = (C.c_void_p * world)()
+created, connected = threading.Barrier(world), threading.Barrier(world)
+failures = []
+def run(rank):
+    try:
+        assert lib.h3_gpu_select_device(rank, err, 256), err.value
+        g = native.Native()
+        x = C.c_void_p()
+        assert lib.h3b_exchange_create(g.gpu, rank, world, rows * H * D, 4, C.byref(x), (C.c_ubyte * 64)()), g.error()
+        exchanges[rank] = x
+        created.wait(60)
+        assert lib.h3b_exchange_connect_local(x, exchanges), g.error()
+        connected.wait(60)
+        srcs = [g.tensor(t.reshape(world, rows, H, D)[rank]) for t in full]
+        slots = [lib.h3b_exchange_slot(x, i) for i in range(4)]
+        for _ in range(2):
+            assert lib.h3b_exchange_scatter_heads_multi_bf16(x, 3, (C.c_int * 3)(0, 1, 2), (C.c_void_p * 3)(*srcs), rows, H, D), g.error()
+            assert lib.h3b_exchange_sdpa_gather_bf16(x, 3, slots[0], slots[1], slots[2], L, rows, H, scale), g.error()
+            got = oracle.from_bf16(g.read(slots[3], (rows, H, D)))
+            n = plan.valid_rows(rank)
+            assert np.abs(got[:n] - want[0, rank * rows: rank * rows + n]).max() <= 1e-2
+        assert g.device_status() == 0
+        connected.wait(60)          # nobody frees a window a peer may still store into
+        lib.h3b_exchange_free(x)
+        g.close()
+    except BaseException as e:
+        failures.append("rank %%d: %%r" %% (rank, e))
+        created.abort(); connected.abort()
+threads = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+for t in threads: t.start()
+for t in threads: t.join(180)
+assert not failures and not any(t.is_alive() for t in threads), failures
+print("OK local exchange")
+''' % str(ROOT)
+    p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=400)
+    assert p.returncode == 0 and "OK local exchange" in p.stdout, (p.stdout + p.stderr)[-3000:]
 
 
 @pytest.mark.gpu

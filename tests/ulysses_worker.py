@@ -114,6 +114,27 @@ def main():
         fused2 = gpu.read(slots[3], (rows, H, D))
         assert np.array_equal(fused2[:n], gathered[:n]), "attention with fused gather differs"
         assert gpu.device_status() == 0
+    # ---- q, k and v scattered by ONE kernel: the same bytes as three single scatters ----
+    singles = [oracle.ulysses(sh)[rank] for sh in shards]
+    for i in range(3):
+        gpu.call("zero", slots[i])
+    srcs = [gpu.tensor(sh[rank]) for sh in shards]
+    order = (C.c_int * 3)(2, 0, 1)                      # any distinct slots
+    assert lib.h3b_exchange_scatter_heads_multi_bf16(x, 3, order, (C.c_void_p * 3)(*srcs), rows, H, D), gpu.error()
+    for i, slot in enumerate(order):
+        assert np.array_equal(gpu.read(slots[slot], (world * rows, H // world, D)), singles[i]), "multi scatter"
+    assert not lib.h3b_exchange_scatter_heads_multi_bf16(x, 2, (C.c_int * 2)(1, 1), (C.c_void_p * 2)(*srcs[:2]), rows, H, D)
+    # ---- one slot reused back to back with a reader in between (no other exchange between them):
+    # the second scatter may overwrite the slot only after every rank's reader has run ----
+    keep = gpu.empty_bf16(rows * H * D)
+    for round_ in range(6):
+        a, b = srcs[round_ % 3], srcs[(round_ + 1) % 3]
+        assert lib.h3b_exchange_scatter_heads_bf16(x, 0, a, rows, H, D), gpu.error()
+        gpu.call("copy_bf16", keep, 0, slots[0], 0, rows * H * D)          # the reader, queued on the stream
+        assert lib.h3b_exchange_scatter_heads_bf16(x, 0, b, rows, H, D), gpu.error()
+        assert np.array_equal(gpu.read(keep, (world * rows, H // world, D)), singles[round_ % 3]), "reader saw the next exchange"
+        assert np.array_equal(gpu.read(slots[0], (world * rows, H // world, D)), singles[(round_ + 1) % 3])
+    assert gpu.device_status() == 0
     # ---- norm + RoPE fused with the scatter: same bits as norm + RoPE followed by three scatters ----
     half = 48
     qkv = oracle.normal_bf16((world, rows, 3 * H * D), 77, 1.5)   # every rank's rows of the projection
