@@ -32,10 +32,12 @@ SEQ = SEQ_VIDEO + SEQ_AUDIO
 SCALE = float(1.0 / np.sqrt(128.0))
 EXCHANGE_NOTE = "fused peer-memory push kernels; gather fused into the attention epilogue"
 E2E_HEAD_GROUPS = int(os.environ.get("H3B_E2E_GROUPS", "6"))   # head groups of the pipelined host-buffer call (4 heads each at H=24)
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dense kernel: the ncu capture
-# summarised in profiles/ measured 384.8 MB at L=16,384, H=24 (algorithmic 402.7 MB; part of the
-# output was still in L2 at kernel end); traffic grows with L*H, so per row of one head:
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dense kernel, measured by ncu at
+# L=16,384, H=24: 384.8 MB (algorithmic 402.7 MB; part of the output was still in L2 at kernel
+# end). Traffic grows with L*H, so per row of one head:
 DENSE_TRAFFIC_BYTES_PER_ROW_HEAD = 384.8e6 / (16384 * 24)
+PARITY_ROWS = 8            # query rows per rank checked against the FP64 recomputation after the timed region
+PARITY_MAX_ABS, PARITY_MIN_COSINE = 1e-2, 0.9999
 
 
 def peaks():
@@ -80,26 +82,41 @@ class ClockSampler:
         sm = sorted(float(r[1]) for r in rows)
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any("Active" == r[5 + i].strip() for r in rows)]
+        power = sorted(float(r[3]) for r in rows)
+        loaded = [x for x in power if x >= 0.7 * power[-1]]     # the samples taken while the GPU was working
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][2]), "reasons": reasons,
-                "samples": len(rows), "power_w_max": max(float(r[3]) for r in rows)}
+                "samples": len(rows), "power_w_max": power[-1], "power_w_under_load": loaded[len(loaded) // 2]}
 
 
 def cpu_sample(oracle, seed_base=1002, rows=256):
     """CPU baseline on a bounded sample: the first `rows` query rows of the dense workload
-    against all keys, all heads, on every host core. Returns (TFLOP/s, description, cores)."""
+    against all keys, all heads, on every host core. Returns (TFLOP/s, seconds, description, threads)."""
+    threads = oracle.set_threads(os.cpu_count() or 1)   # a launcher may have exported OMP_NUM_THREADS=1
     q = oracle.normal_bf16((rows, HEADS, DIM), seed_base)
     k = oracle.normal_bf16((SEQ, HEADS, DIM), seed_base + 1)
     v = oracle.normal_bf16((SEQ, HEADS, DIM), seed_base + 2)
     seconds = oracle.time_attention(q, k, v, SCALE)
     flops = 4.0 * rows * SEQ * HEADS * DIM
-    sample = "first %d of %d query rows x %d keys x %d heads (%.1f GFLOP), CPU oracle, OpenMP" % (
-        rows, SEQ, SEQ, HEADS, flops / 1e9)
-    return flops / seconds / 1e12, seconds, sample, os.cpu_count()
+    sample = "first %d of %d query rows x %d keys x %d heads (%.1f GFLOP), CPU oracle, OpenMP, %d threads" % (
+        rows, SEQ, SEQ, HEADS, flops / 1e9, threads)
+    return flops / seconds / 1e12, seconds, sample, threads
+
+
+def cpu_c1_full(oracle):
+    """Benchmark configuration 1 in full on the host cores: L=4096, H=8 (68.7 GFLOP)."""
+    threads = oracle.set_threads(os.cpu_count() or 1)
+    q, k, v = (oracle.normal_bf16((4096, 8, DIM), 1001 + i) for i in range(3))
+    oracle.time_attention(q[:64], k, v, SCALE)   # warm the threads
+    seconds = oracle.time_attention(q, k, v, SCALE)
+    flops = 4.0 * 4096 * 4096 * 8 * DIM
+    return {"workload": "L=4096, H=8, D=128 in full (68.7 GFLOP)", "seconds": seconds,
+            "tflops": flops / seconds / 1e12, "threads": threads}
 
 
 def run_reference(args):
     """The reference has no CPU attention path; its arm is the CPU oracle (a port of the
-    reference's FP32 attention arithmetic) on all host threads, on a bounded sample per step."""
+    reference's FP32 attention arithmetic) on all host threads, on a bounded sample per step.
+    Only rank 0 works; the thread count is set explicitly and the one in effect is reported."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -107,7 +124,7 @@ def run_reference(args):
     oracle.build()
     values = []
     for i in range(args.warmup + args.steps):
-        tflops, seconds, sample, cores = cpu_sample(oracle, rows=64)
+        tflops, seconds, sample, threads = cpu_sample(oracle, rows=64)
         if i >= args.warmup:
             values.append((tflops, seconds))
     value = float(np.mean([v[0] for v in values]))
@@ -117,7 +134,7 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -140,7 +157,7 @@ def main():
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="dense", choices=["dense", "vsa", "live", "producer"])
+    parser.add_argument("--workload", default="dense", choices=["dense", "vsa", "live", "producer", "comparators"])
     parser.add_argument("--no-also", action="store_true", help="skip the secondary measurements")
     parser.add_argument("--exchange", default="push", choices=["push", "nccl"],
                         help="N>1: fused peer-memory exchange kernel (default) or transpose + NCCL send/recv")
@@ -153,6 +170,8 @@ def main():
         EXCHANGE_NOTE = "transpose kernel + NCCL send/recv"
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "comparators":
+        return run_comparators()
 
     import torch
     import torch.distributed as dist
@@ -223,23 +242,21 @@ def main():
         gpu.close()
         return
 
+    env = Env(gpu, torch, dist if world > 1 else None, device, stream, world, rank, comm, barrier, max_over_ranks)
     plan = ulysses.plan(SEQ, HEADS, world)
     rows, local_heads = plan.shard_rows, plan.local_heads
     shard_elems = rows * HEADS * DIM
 
-    # Seeded synthetic inputs: the full tensors are defined by (seed, element index); each rank
-    # generates its own row shard. Host copies live in pinned memory for the end-to-end leg.
-    def make_shard(seed):
-        g = torch.Generator(device="cpu")
-        g.manual_seed(seed * 1000 + rank)
-        x = torch.randn(rows, HEADS, DIM, generator=g, dtype=torch.float32).to(torch.bfloat16)
-        if plan.valid_rows(rank) < rows:
-            x[plan.valid_rows(rank):] = 0
-        return x.pin_memory()
-
-    host_q, host_k, host_v = make_shard(1002), make_shard(1003), make_shard(1004)
+    # Seeded synthetic inputs: the FULL tensors are a function of the seed alone (every rank draws
+    # them with the same device generator); a rank keeps its row shard on the device and in pinned
+    # host memory (for the end-to-end leg), and K and V in full on the host for the parity check.
+    full = [env.full_tensor(plan, HEADS, seed) for seed in (1002, 1003, 1004)]
+    host_kv = [env.to_host_bits(x[:SEQ]) for x in full[1:]]
+    shard = lambda x: x[rank * rows:(rank + 1) * rows].contiguous()
+    dq, dk, dv = (shard(x) for x in full)
+    host_q, host_k, host_v = (x.cpu().pin_memory() for x in (dq, dk, dv))
     host_o = torch.empty(rows, HEADS, DIM, dtype=torch.bfloat16).pin_memory()
-    dq, dk, dv = (x.to(device, non_blocking=True) for x in (host_q, host_k, host_v))
+    del full
     do = torch.empty_like(dq)
     scratch = torch.empty_like(dq) if world > 1 else None
     work = [torch.empty_like(dq) for _ in range(3)] if world > 1 else None
@@ -253,21 +270,12 @@ def main():
 
     exchange, slots = None, None
     if world > 1 and args.exchange == "push":
-        # windows of four tensors (Q, K, V, gathered O) per rank, handles all-gathered through torch
-        xh = C.c_void_p()
-        handle = (C.c_ubyte * 64)()
-        if not lib.h3b_exchange_create(gpu.gpu, rank, world, shard_elems, 4, C.byref(xh), handle):
-            raise RuntimeError(gpu.error())
-        mine = torch.tensor(list(handle), dtype=torch.uint8, device=device)
-        everyone = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(everyone, mine)
-        if not lib.h3b_exchange_connect(xh, bytes(torch.cat(everyone).cpu().tolist())):
-            raise RuntimeError(gpu.error())
-        exchange = xh
-        slots = [C.c_void_p(lib.h3b_exchange_slot(xh, i)) for i in range(4)]
-        dist.barrier()
+        # windows of five tensors per rank: Q, K, V and two gathered-output slots (the end-to-end
+        # leg alternates them so that a copy-out can overlap the next head group's attention)
+        exchange, slots = env.make_exchange(shard_elems, 5)
 
     launches = [0]
+    three = (C.c_int * 3)(0, 1, 2)
 
     def attention_step():
         """The hot path with inputs resident in HBM."""
@@ -276,15 +284,15 @@ def main():
             launches[0] += 1
             return
         if exchange is not None:
-            # one kernel per exchange: local tensor -> final layout in the owners' windows
-            for i, t in enumerate((tq, tk, tv)):
-                if not lib.h3b_exchange_scatter_heads_bf16(exchange, i, t, rows, HEADS, DIM):
-                    raise RuntimeError(gpu.error())
+            # ONE kernel scatters q, k and v: local tensors -> final layout in the owners' windows
+            if not lib.h3b_exchange_scatter_heads_multi_bf16(exchange, 3, three, (C.c_void_p * 3)(tq, tk, tv), rows,
+                                                             HEADS, DIM):
+                raise RuntimeError(gpu.error())
             # attention stores each output row straight into its owner's window (slot 3)
             if not lib.h3b_exchange_sdpa_gather_bf16(exchange, 3, slots[0], slots[1], slots[2], SEQ, rows,
                                                      HEADS, SCALE):
                 raise RuntimeError(gpu.error())
-            launches[0] += 5
+            launches[0] += 4          # scatter; open, attention, close
             return
         # the NCCL exchange is in place, so each step scatters a fresh copy of the row shards
         for w, src in zip(work, (dq, dk, dv)):
@@ -295,6 +303,9 @@ def main():
         gpu.call("ulysses_gather_heads_bf16", comm, to, tscr, rows, HEADS, DIM)
         launches[0] += 5
 
+    pipe = HostPipeline(env, exchange, slots, rows, (host_q, host_k, host_v), host_o) \
+        if exchange is not None and HEADS % (3 * world) == 0 else None
+
     def e2e_step():
         """The same step through the public API with host buffers."""
         if world == 1:
@@ -304,12 +315,14 @@ def main():
                 raise RuntimeError(gpu.error())
             launches[0] += E2E_HEAD_GROUPS + (2 if HEADS // E2E_HEAD_GROUPS >= 2 else 0)   # edge groups run as two halves
             return
+        if pipe is not None:
+            pipe.step()
+            return
         dq.copy_(host_q, non_blocking=True)
         dk.copy_(host_k, non_blocking=True)
         dv.copy_(host_v, non_blocking=True)
         attention_step()
         if exchange is not None:
-            # the gathered output lives in window slot 3
             if not lib.h3_gpu_download(gpu.gpu, slots[3], 0, host_o.data_ptr(), shard_elems * 2):
                 raise RuntimeError(gpu.error())
             return
@@ -337,6 +350,12 @@ def main():
     ms = timed(attention_step, args.steps, args.warmup)
     counted = launches[0] * args.steps // (args.steps + args.warmup)
 
+    # ---- parity, after the timed region: sampled rows of this rank's output against the FP64
+    # recomputation on the full seeded Q, K, V; the worst figures over all ranks are reported ----
+    out_rows = env.to_host_bits(gpu_tensor_view(torch, slots[3], gpu, rows, HEADS) if exchange is not None else do)
+    parity = env.parity_rows(out_rows, env.to_host_bits(dq), host_kv[0], host_kv[1], rank * rows,
+                             plan.valid_rows(rank), SCALE)
+
     # kernel-only duration of the dense kernel (the dominant kernel), events on its own stream
     def kernel_only():
         if world == 1:
@@ -352,7 +371,14 @@ def main():
         return start.elapsed_time(stop) / args.steps
 
     kernel_ms = kernel_only()
+    # what the exchanges add to a step, from CUDA events (no profiler around a multi-rank command)
+    exchange_ms = ms - max_over_ranks(kernel_ms) if world > 1 else 0.0
     e2e_ms = timed(e2e_step, max(2, args.steps // 2), 1)
+    if pipe is not None:
+        e2e_parity = env.parity_rows(env.tensor_bits(host_o), env.to_host_bits(dq), host_kv[0], host_kv[1],
+                                     rank * rows, plan.valid_rows(rank), SCALE, sample=4)
+    else:
+        e2e_parity = None
     if ms * (args.steps + args.warmup) < 1500.0:
         # every rank keeps its device busy with the same step (ms is the max over ranks, so all
         # ranks agree) until the sampler on rank 0 has seen about a second of load
@@ -367,44 +393,62 @@ def main():
     pk = peaks()
     kernel_flops = flops / world
     achieved = kernel_flops / (kernel_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "attn_tc5_pair_kernel", "achieved": achieved,
+                "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
+                "peak_source": pk["source"] + " burst", "frac_of_sustained": achieved / pk["tflops_sustained"],
+                "frac_of_nominal_2250": achieved / 2250.0, "kernel_ms": kernel_ms,
+                "flops_per_launch": kernel_flops,
+                "traffic": DENSE_TRAFFIC_BYTES_PER_ROW_HEAD * SEQ * HEADS / world}
+    if clocks and clocks.get("sm_mhz"):
+        # the board sits at its power limit in this loop: the same kernel at the maximum clock,
+        # and the energy one step takes, make variants comparable across runs
+        roofline["achieved_at_max_clock"] = achieved * clocks["sm_max_mhz"] / clocks["sm_mhz"]
+        roofline["joules_per_step_rank0"] = clocks["power_w_under_load"] * ms * 1e-3
     line = {
         "metric": "attn_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(world),
-        "roofline": {"bound": "tensor", "kernel": "attn_tc5_pair_kernel", "achieved": achieved,
-                     "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
-                     "peak_source": pk["source"] + " burst", "frac_of_sustained": achieved / pk["tflops_sustained"],
-                     "frac_of_nominal_2250": achieved / 2250.0, "kernel_ms": kernel_ms,
-                     "flops_per_launch": kernel_flops,
-                     "traffic": DENSE_TRAFFIC_BYTES_PER_ROW_HEAD * SEQ * HEADS / world},
+        "roofline": roofline,
         "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": 3 * shard_elems * 2, "d2h_bytes_per_step": shard_elems * 2,
                 "api": "h3b_sdpa_bf16_host (pinned host buffers, %d pipelined head groups)" % E2E_HEAD_GROUPS
-                       if world == 1 else "pinned copies + ulysses scatter/sdpa/gather primitives"},
+                       if world == 1 else
+                       ("pinned host shards, 3 head groups pipelined: 2-D copy-in | fused scatter + attention with "
+                        "fused gather | copy-out" if pipe is not None else
+                        "pinned copies + ulysses scatter/sdpa/gather primitives"),
+                "parity": e2e_parity},
+        "parity": parity,
         "gpu_launches": counted,
         "clocks": clocks,
     }
+    if world > 1:
+        line["step_split_ms"] = {"attention_kernel": kernel_ms, "exchanges_and_handshakes": exchange_ms}
+    if not parity["ok"] or (e2e_parity is not None and not e2e_parity["ok"]):
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        raise SystemExit("parity check failed: %r / %r" % (parity, e2e_parity))
 
-    dit = None
+    also = {}
     if not args.no_also and not args.sequence:
-        dit = dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_over_ranks,
-                       exchange=exchange, slots=slots)
-    vsa_sharded = None
-    if not args.no_also and not args.sequence and world > 1 and exchange is not None:
-        vsa_sharded = vsa_step_sharded(gpu, torch, dist, device, stream, world, rank, barrier, max_over_ranks)
+        also["dit_step"] = dit_step(env, plan, HEADS)
+        if 56 % world == 0:
+            # the reference's own head count (h3_dit.c:23) beside the benchmark's 24
+            also["dit_step_h56"] = dit_step(env, ulysses.plan(SEQ, 56, world), 56, steps=1)
+        if world > 1 and exchange is not None:
+            also["vsa_step"] = vsa_step_sharded(env)
+            also["c4_step"] = c4_step(env)
     if rank == 0 and world == 1:
         oracle = entry.load_oracle()
         oracle.build()
-        tflops, seconds, sample, cores = cpu_sample(oracle)
-        line["cpu_baseline"] = {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                                "sample": sample, "seconds": seconds}
+        tflops, seconds, sample, threads = cpu_sample(oracle)
+        line["cpu_baseline"] = {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                "sample": sample, "seconds": seconds, "c1_in_full": cpu_c1_full(oracle)}
         if not args.no_also and not args.sequence:
-            line["also"] = secondary(gpu, torch, device, stream, pk)
-    if dit is not None:
-        line.setdefault("also", {})["dit_step"] = dit
-    if vsa_sharded is not None:
-        line.setdefault("also", {})["vsa_step"] = vsa_sharded
+            also.update(secondary(gpu, torch, device, stream, pk))
+            also["comparators"] = comparators_in_child()
+    if also:
+        line["also"] = also
     if rank == 0:
         print(json.dumps(line), flush=True)
     if exchange is not None:
@@ -418,17 +462,183 @@ def main():
         dist.destroy_process_group()
 
 
-def dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_over_ranks, blocks=50, steps=2,
-             exchange=None, slots=None):
+def gpu_tensor_view(torch, handle, gpu, rows, heads):
+    """torch view of a library tensor (an exchange slot) holding [rows][heads][128] bf16."""
+    pointer = gpu.lib.h3b_tensor_data(handle)
+    n = rows * heads * DIM
+
+    class _Array:   # the CUDA array interface is the one zero-copy door torch offers for a raw pointer
+        __cuda_array_interface__ = {"shape": (n,), "typestr": "<i2", "data": (pointer, False), "version": 3}
+    return torch.as_tensor(_Array(), device="cuda").view(torch.bfloat16).view(rows, heads, DIM)
+
+
+class Env:
+    """What every leg of the benchmark needs: the context, torch, the process group, helpers."""
+
+    def __init__(self, gpu, torch, dist, device, stream, world, rank, comm, barrier, max_over_ranks):
+        self.gpu, self.torch, self.dist, self.device, self.stream = gpu, torch, dist, device, stream
+        self.world, self.rank, self.comm, self.barrier, self.max_over_ranks = world, rank, comm, barrier, max_over_ranks
+        self.lib = gpu.lib
+
+    def wrap(self, t):
+        return self.gpu.wrap(t.data_ptr(), t.numel())
+
+    def full_tensor(self, plan, heads, seed, sigma=1.0):
+        """The whole [padded rows][heads][128] tensor of a seed, zero behind the valid rows; the
+        same bits on every rank."""
+        torch = self.torch
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+        x = torch.randn(plan.padded_rows, heads, DIM, generator=g, device=self.device, dtype=torch.float32)
+        if sigma != 1.0:
+            x *= sigma
+        x = x.to(torch.bfloat16)
+        x[plan.sequence:] = 0
+        return x
+
+    def tensor_bits(self, t):
+        return t.view(self.torch.int16).numpy().view(np.uint16)
+
+    def to_host_bits(self, t):
+        """bf16 torch tensor -> numpy uint16 bit patterns on the host."""
+        self.torch.cuda.synchronize()
+        return t.contiguous().view(self.torch.int16).cpu().numpy().view(np.uint16)
+
+    def make_exchange(self, slot_elements, count):
+        """A window of `count` slots on every rank, handles all-gathered through torch.distributed."""
+        lib, torch, dist = self.lib, self.torch, self.dist
+        xh, handle = C.c_void_p(), (C.c_ubyte * 64)()
+        if not lib.h3b_exchange_create(self.gpu.gpu, self.rank, self.world, slot_elements, count, C.byref(xh), handle):
+            raise RuntimeError(self.gpu.error())
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.device)
+        everyone = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(everyone, mine)
+        if not lib.h3b_exchange_connect(xh, bytes(torch.cat(everyone).cpu().tolist())):
+            raise RuntimeError(self.gpu.error())
+        slots = [C.c_void_p(lib.h3b_exchange_slot(xh, i)) for i in range(count)]
+        dist.barrier()
+        return xh, slots
+
+    def free_exchange(self, xh, slots):
+        self.torch.cuda.synchronize()
+        self.dist.barrier()
+        for t in slots:
+            self.lib.h3_gpu_tensor_free(t)
+        self.lib.h3b_exchange_free(xh)
+
+    def parity_rows(self, out_bits, q_bits, k_bits, v_bits, first_row, valid, scale, sample=PARITY_ROWS):
+        """out_bits, q_bits: this rank's [rows][H][128] output and query rows (bit patterns);
+        k_bits, v_bits: all keys and values. `sample` rows of the shard (spread over it, the first
+        and the last valid one included) are recomputed in FP64 by the CPU oracle; the worst
+        max-abs error and cosine over all ranks are returned."""
+        oracle = entry.load_oracle()
+        oracle.build()
+        oracle.set_threads(max(1, (os.cpu_count() or 1) // self.world))
+        worst, cosine = 0.0, 1.0
+        if valid > 0:
+            picks = np.unique(np.linspace(0, valid - 1, sample).astype(np.int64))
+            want = oracle.attention_rows_f64(np.arange(len(picks)), q_bits[picks], k_bits, v_bits, scale)
+            got = oracle.from_bf16(out_bits[picks]).astype(np.float64)
+            want = want.astype(np.float64)
+            worst = float(np.abs(got - want).max())
+            cosine = float((got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want) + 1e-300))
+            if not np.isfinite(got).all():
+                worst = float("inf")
+        if self.world > 1:
+            t = self.torch.tensor([worst, -cosine], device=self.device, dtype=self.torch.float64)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            worst, cosine = float(t[0].item()), -float(t[1].item())
+        return {"rows_per_rank": sample, "ranks": self.world, "max_abs": worst, "min_cosine": cosine,
+                "against": "FP64 recomputation of the sampled rows (CPU oracle) on the full seeded Q, K, V",
+                "limits": {"max_abs": PARITY_MAX_ABS, "cosine": PARITY_MIN_COSINE},
+                "ok": bool(worst <= PARITY_MAX_ABS and cosine >= PARITY_MIN_COSINE)}
+
+    def events(self, fn, steps, warmup):
+        torch = self.torch
+        for _ in range(warmup):
+            fn()
+        self.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(self.stream)
+        for _ in range(steps):
+            fn()
+        b.record(self.stream)
+        self.barrier()
+        return self.max_over_ranks(a.elapsed_time(b) / steps)
+
+
+class HostPipeline:
+    """End-to-end step at N > 1 from pinned host shards: the 24 heads go through in three groups of
+    eight, and copy-in (2-D strided copies on one stream), fused scatter + attention with fused
+    gather (the context's stream) and copy-out (a third stream) of consecutive groups overlap.
+    Two staging slots for the inputs, two window slots for the gathered output."""
+    GROUPS = 3
+
+    def __init__(self, env, exchange, slots, rows, host_in, host_out):
+        torch = env.torch
+        self.env, self.exchange, self.slots, self.rows = env, exchange, slots, rows
+        self.host_in, self.host_out = host_in, host_out
+        self.heads = HEADS // self.GROUPS
+        self.cudart = C.CDLL("libcudart.so.12")
+        self.cudart.cudaMemcpy2DAsync.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t,
+                                                  C.c_size_t, C.c_int, C.c_void_p]
+        self.h2d, self.d2h = torch.cuda.Stream(env.device), torch.cuda.Stream(env.device)
+        self.stage = [[torch.empty(rows, self.heads, DIM, device=env.device, dtype=torch.bfloat16) for _ in range(3)]
+                      for _ in range(2)]
+        self.wrapped = [[env.wrap(t) for t in s] for s in self.stage]
+        self.loaded = [torch.cuda.Event() for _ in range(2)]
+        self.computed = [torch.cuda.Event() for _ in range(2)]
+        self.stored = [torch.cuda.Event() for _ in range(2)]
+        self.used = [False, False]
+
+    def copy2d(self, dst, dpitch, src, spitch, width, height, kind, stream):
+        code = self.cudart.cudaMemcpy2DAsync(dst, dpitch, src, spitch, width, height, kind, stream.cuda_stream)
+        if code:
+            raise RuntimeError("cudaMemcpy2DAsync: %d" % code)
+
+    def step(self):
+        env, lib, rows, hg = self.env, self.env.lib, self.rows, self.heads
+        pitch, width = HEADS * DIM * 2, hg * DIM * 2
+        first = env.torch.cuda.Event()
+        first.record(env.stream)
+        self.h2d.wait_event(first)          # everything already queued on the context's stream comes first
+        for g in range(self.GROUPS):
+            s = g & 1
+            if self.used[s]:
+                self.h2d.wait_event(self.computed[s])      # the staging slot's previous group has been scattered
+                env.stream.wait_event(self.stored[s])      # the output slot's previous group has been copied out
+            for t in range(3):
+                self.copy2d(self.stage[s][t].data_ptr(), width, self.host_in[t].data_ptr() + g * width, pitch, width,
+                            rows, 1, self.h2d)
+            self.loaded[s].record(self.h2d)
+            env.stream.wait_event(self.loaded[s])
+            if not lib.h3b_exchange_scatter_heads_multi_bf16(self.exchange, 3, (C.c_int * 3)(0, 1, 2),
+                                                             (C.c_void_p * 3)(*self.wrapped[s]), rows, hg, DIM):
+                raise RuntimeError(env.gpu.error())
+            if not lib.h3b_exchange_sdpa_gather_bf16(self.exchange, 3 + s, self.slots[0], self.slots[1], self.slots[2],
+                                                     SEQ, rows, hg, SCALE):
+                raise RuntimeError(env.gpu.error())
+            self.computed[s].record(env.stream)
+            self.d2h.wait_event(self.computed[s])
+            self.copy2d(self.host_out.data_ptr() + g * width, pitch, lib.h3b_tensor_data(self.slots[3 + s]), width,
+                        width, rows, 2, self.d2h)
+            self.stored[s].record(self.d2h)
+            self.used[s] = True
+        self.d2h.synchronize()
+        env.stream.synchronize()
+
+
+def dit_step(env, plan, heads, blocks=50, steps=2):
     """One denoising step of the 50-block DiT at the benchmark shape, timed at N GPUs.
 
     Op order of the reference's run_block (h3_dit.c:2450-2673) with the reference's widths
-    (hidden 5376, FFN 14336, h3_dit.c:20-35) and the benchmark's 24 heads. Q/K norm + RoPE, attention
-    and the Ulysses exchanges are this library's; the projections and MLP are torch bf16 GEMMs and
-    the other elementwise ops (AdaLN, SwiGLU, gates) are plain torch ops standing in for
-    the reference's own kernels, which are outside this library. One block's synthetic weights
-    are reused for all blocks. Reported for the scaling picture only."""
-    hidden, ffn, inner = 5376, 14336, HEADS * DIM
+    (hidden 5376, FFN 14336, h3_dit.c:20-35). Q/K norm + RoPE, attention and the Ulysses
+    exchanges are this library's; the projections and MLP are torch bf16 GEMMs and the other
+    elementwise ops (AdaLN, SwiGLU, gates) are plain torch ops standing in for the reference's
+    own kernels, which are outside this library. One block's synthetic weights are reused for
+    all blocks. Reported for the scaling picture only."""
+    gpu, torch, device, stream, world, lib = env.gpu, env.torch, env.device, env.stream, env.world, env.lib
+    hidden, ffn, inner = 5376, 14336, heads * DIM
     rows, local_heads = plan.shard_rows, plan.local_heads
     g = torch.Generator(device=device)
     g.manual_seed(4242)
@@ -437,133 +647,215 @@ def dit_step(gpu, torch, device, stream, plan, comm, world, rank, barrier, max_o
     w_fc1, w_fc2 = rand(hidden, 2 * ffn, fan=hidden), rand(ffn, hidden, fan=ffn)
     mod = (0.1 * torch.randn(6, hidden, generator=g, device=device)).to(torch.bfloat16)
     x0 = torch.randn(rows, hidden, generator=g, device=device).to(torch.bfloat16)
-    q, k, v = (torch.empty(rows, HEADS, DIM, device=device, dtype=torch.bfloat16) for _ in range(3))
+    q, k, v = (torch.empty(rows, heads, DIM, device=device, dtype=torch.bfloat16) for _ in range(3))
     o = torch.empty_like(q)
-    scratch = torch.empty_like(q)
     gathered = torch.empty(world * rows, hidden, device=device, dtype=torch.bfloat16) if world > 1 else None
-    wrap = lambda t: gpu.wrap(t.data_ptr(), t.numel())
-    tq, tk, tv, to, tscr = wrap(q), wrap(k), wrap(v), wrap(o), wrap(scratch)
+    tq, tk, tv, to = (env.wrap(t) for t in (q, k, v, o))
     rope_tensors = rope_tables(torch, device, g, rows)   # kept alive: the wrappers do not own them
-    rope = [wrap(t) for t in rope_tensors]
+    rope = [env.wrap(t) for t in rope_tensors]
     F = torch.nn.functional
-    lib = gpu.lib
+    exchange, slots = env.make_exchange(rows * heads * DIM, 4) if world > 1 else (None, None)
+    scale = float(1.0 / np.sqrt(128.0))
 
-    def norm_mod(x, scale, shift):
-        return F.rms_norm(x, (hidden,)) * (1 + scale) + shift
+    def norm_mod(x, scale_, shift):
+        return F.rms_norm(x, (hidden,)) * (1 + scale_) + shift
 
     def forward():
         x = x0.clone()
         for _ in range(blocks):
             h = norm_mod(x, mod[0], mod[1])
             qkv = h @ w_qkv                               # [rows][q|k|v][head][128]
-            tqkv = wrap(qkv)
+            tqkv = env.wrap(qkv)
             if exchange is not None:
                 # norm + RoPE store straight into the owners' head shards
-                if not lib.h3b_exchange_qkv_rope_scatter_bf16(exchange, 0, 1, 2, tqkv, *rope, rows, HEADS, 48,
+                if not lib.h3b_exchange_qkv_rope_scatter_bf16(exchange, 0, 1, 2, tqkv, *rope, rows, heads, 48,
                                                               1e-5, 0):
                     raise RuntimeError(gpu.error())
                 if not lib.h3b_exchange_sdpa_gather_bf16(exchange, 3, slots[0], slots[1], slots[2], plan.sequence,
-                                                         rows, HEADS, SCALE):
+                                                         rows, heads, scale):
                     raise RuntimeError(gpu.error())
-                gpu.call("copy_bf16", to, 0, slots[3], 0, rows * HEADS * DIM)   # window -> torch tensor
+                gpu.call("copy_bf16", to, 0, slots[3], 0, rows * heads * DIM)   # window -> torch tensor
             else:
-                gpu.call("qkv_rope_bf16", tq, tk, tv, tqkv, *rope, rows, HEADS, DIM, 48, 1e-5)
-                if world > 1:
-                    for t in (tq, tk, tv):
-                        gpu.call("ulysses_scatter_heads_bf16", comm, t, tscr, rows, HEADS, DIM)
-                gpu.call("sdpa_bf16", to, tq, tk, tv, plan.sequence, local_heads, DIM, SCALE)
-                if world > 1:
-                    gpu.call("ulysses_gather_heads_bf16", comm, to, tscr, rows, HEADS, DIM)
+                gpu.call("qkv_rope_bf16", tq, tk, tv, tqkv, *rope, rows, heads, DIM, 48, 1e-5)
+                gpu.call("sdpa_bf16", to, tq, tk, tv, plan.sequence, local_heads, DIM, scale)
             gpu.free(tqkv)
             x = x + mod[2] * (o.view(rows, inner) @ w_out)
             h = norm_mod(x, mod[3], mod[4])
             u = h @ w_fc1
             x = x + mod[5] * ((F.silu(u[:, :ffn]) * u[:, ffn:]) @ w_fc2)
         if world > 1:
-            tx, tg = wrap(x), wrap(gathered)
-            gpu.call("all_gather_bf16", comm, tg, tx, rows * hidden)
+            tx, tg = env.wrap(x), env.wrap(gathered)
+            gpu.call("all_gather_bf16", env.comm, tg, tx, rows * hidden)
         return x
 
-    forward()
-    barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record(stream)
-    for _ in range(steps):
-        forward()
-    b.record(stream)
-    barrier()
-    ms = max_over_ranks(a.elapsed_time(b) / steps)
+    ms = env.events(forward, steps, 1)
+    if exchange is not None:
+        env.free_exchange(exchange, slots)
     gemm_flops = 2.0 * plan.sequence * (hidden * 3 * inner + inner * hidden + hidden * 2 * ffn + ffn * hidden) * blocks
-    attn_flops = 4.0 * plan.sequence ** 2 * HEADS * DIM * blocks
+    attn_flops = 4.0 * plan.sequence ** 2 * heads * DIM * blocks
     return {"workload": "50-block DiT denoising step, L=%d, H=%d, hidden %d, FFN %d; norm/RoPE, attention, Ulysses "
-                        "exchanges from this library; GEMMs and other elementwise ops torch" % (plan.sequence, HEADS, hidden, ffn),
+                        "exchanges from this library; GEMMs and other elementwise ops torch" % (plan.sequence, heads, hidden, ffn),
             "ms_per_step": ms, "n_gpus": world, "steps": steps, "blocks": blocks,
             "model_tflops": (gemm_flops + attn_flops) / ms / 1e9}
 
 
-def vsa_step_sharded(gpu, torch, dist, device, stream, world, rank, barrier, max_over_ranks, steps=5):
-    """Video sparse attention at N GPUs (reference h3_dit.c:2496-2546): this rank's rows of q, k, v
-    and the gate are scattered to head shards with the fused exchange, VSA runs on heads/N heads
-    over the whole sequence, the output is gathered back to row shards."""
+def c4_step(env, steps=3):
+    """The ten-second clip of the benchmark's Ulysses configuration: L = 62*1620 + 1024 = 101,464
+    rows, H = 24, row-sharded; one fused scatter of q, k, v and the attention with fused gather per
+    step, with the same sampled-row parity check as the main workload."""
     from h3_omni_b200 import ulysses
-    lib = gpu.lib
+    gpu, torch, lib, world, rank = env.gpu, env.torch, env.lib, env.world, env.rank
+    sequence = 62 * 1620 + 1024
+    plan = ulysses.plan(sequence, HEADS, world)
+    rows = plan.shard_rows
+    full = [env.full_tensor(plan, HEADS, seed) for seed in (1004, 1014, 1024)]
+    host_kv = [env.to_host_bits(x[:sequence]) for x in full[1:]]
+    shards = [x[rank * rows:(rank + 1) * rows].contiguous() for x in full]
+    del full
+    handles = (C.c_void_p * 3)(*[env.wrap(t) for t in shards])
+    exchange, slots = env.make_exchange(rows * HEADS * DIM, 4)
+
+    def step():
+        if not lib.h3b_exchange_scatter_heads_multi_bf16(exchange, 3, (C.c_int * 3)(0, 1, 2), handles, rows, HEADS, DIM):
+            raise RuntimeError(gpu.error())
+        if not lib.h3b_exchange_sdpa_gather_bf16(exchange, 3, slots[0], slots[1], slots[2], sequence, rows, HEADS, SCALE):
+            raise RuntimeError(gpu.error())
+
+    ms = env.events(step, steps, 2)
+    out = env.to_host_bits(gpu_tensor_view(torch, slots[3], gpu, rows, HEADS))
+    parity = env.parity_rows(out, env.to_host_bits(shards[0]), host_kv[0], host_kv[1], rank * rows,
+                             plan.valid_rows(rank), SCALE, sample=4)
+    env.free_exchange(exchange, slots)
+    flops = 4.0 * sequence * sequence * HEADS * DIM
+    return {"workload": "dense joint attention of a 10 s clip, L=%d, H=%d over %d GPUs (fused scatter of q, k, v; "
+                        "attention with fused gather)" % (sequence, HEADS, world),
+            "ms_per_step": ms, "tflops": flops / ms / 1e9, "n_gpus": world, "steps": steps, "parity": parity}
+
+
+def vsa_step_sharded(env, steps=5):
+    """Video sparse attention at N GPUs (reference h3_dit.c:2496-2546): this rank's rows of q, k, v
+    and the gate are scattered to head shards by ONE fused exchange kernel, VSA runs on heads/N
+    heads over the whole sequence, the output is gathered back to row shards. After the timed
+    loop the gathered rows are compared, bit for bit, with the same call on all heads on one GPU."""
+    from h3_omni_b200 import ulysses
+    gpu, torch, lib, world, rank, device = env.gpu, env.torch, env.lib, env.world, env.rank, env.device
     text, audio, grid = 64, 512, (32, 30, 54)
     sequence = text + audio + grid[0] * grid[1] * grid[2]
     plan = ulysses.plan(sequence, HEADS, world)
     rows, hg = plan.shard_rows, plan.local_heads
-    g = torch.Generator(device=device)
-    g.manual_seed(1003 * 1000 + rank)
-    shard = [torch.randn(rows, HEADS, DIM, generator=g, device=device).to(torch.bfloat16) for _ in range(3)]
-    shard.append((0.3 * torch.randn(rows, HEADS, DIM, generator=g, device=device)).to(torch.bfloat16))
-    for t in shard:
-        t[plan.valid_rows(rank):] = 0
-    xh, handle = C.c_void_p(), (C.c_ubyte * 64)()
-    if not lib.h3b_exchange_create(gpu.gpu, rank, world, rows * HEADS * DIM, 5, C.byref(xh), handle):
-        raise RuntimeError(gpu.error())
-    mine = torch.tensor(list(handle), dtype=torch.uint8, device=device)
-    everyone = [torch.empty_like(mine) for _ in range(world)]
-    dist.all_gather(everyone, mine)
-    if not lib.h3b_exchange_connect(xh, bytes(torch.cat(everyone).cpu().tolist())):
-        raise RuntimeError(gpu.error())
-    slots = [C.c_void_p(lib.h3b_exchange_slot(xh, i)) for i in range(5)]
+    full = [env.full_tensor(plan, HEADS, 1003 + 10 * i, 0.3 if i == 3 else 1.0) for i in range(4)]
+    shard = [x[rank * rows:(rank + 1) * rows].contiguous() for x in full]
+    exchange, slots = env.make_exchange(rows * HEADS * DIM, 5)
     vsa = gpu.call("vsa_new", text, audio, *grid, hg)
     info = [C.c_int() for _ in range(4)]
     lib.h3b_vsa_info(vsa, *[C.byref(x) for x in info])
     tiles, prefix = info[1].value, info[2].value
-    lib.h3b_vsa_set_keep(vsa, (tiles - prefix) // 8)
+    keep = (tiles - prefix) // 8
+    lib.h3b_vsa_set_keep(vsa, keep)
     local_out = torch.zeros(world * rows, hg, DIM, device=device, dtype=torch.bfloat16)
-    tshard = [gpu.wrap(t.data_ptr(), t.numel()) for t in shard]
-    tout = gpu.wrap(local_out.data_ptr(), local_out.numel())
-    dist.barrier()
+    tshard = (C.c_void_p * 4)(*[env.wrap(t) for t in shard])
+    tout = env.wrap(local_out)
+    four = (C.c_int * 4)(0, 1, 2, 3)
 
     def step():
-        for i, t in enumerate(tshard):
-            if not lib.h3b_exchange_scatter_heads_bf16(xh, i, t, rows, HEADS, DIM):
-                raise RuntimeError(gpu.error())
+        if not lib.h3b_exchange_scatter_heads_multi_bf16(exchange, 4, four, tshard, rows, HEADS, DIM):
+            raise RuntimeError(gpu.error())
         if not lib.h3_gpu_vsa_bf16(vsa, tout, slots[0], slots[1], slots[2], slots[3]):
             raise RuntimeError(gpu.error())
-        if not lib.h3b_exchange_gather_heads_bf16(xh, 4, tout, rows, HEADS, DIM):
+        if not lib.h3b_exchange_gather_heads_bf16(exchange, 4, tout, rows, HEADS, DIM):
             raise RuntimeError(gpu.error())
 
-    for _ in range(2):
-        step()
-    barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record(stream)
-    for _ in range(steps):
-        step()
-    b.record(stream)
-    barrier()
-    ms = max_over_ranks(a.elapsed_time(b) / steps)
+    ms = env.events(step, steps, 2)
+    # parity: all heads on this one GPU, the rows of this rank's shard must come out bit-identical
+    whole = gpu.call("vsa_new", text, audio, *grid, HEADS)
+    lib.h3b_vsa_set_keep(whole, keep)
+    whole_out = torch.empty(sequence, HEADS, DIM, device=device, dtype=torch.bfloat16)
+    ins = [env.wrap(x[:sequence]) for x in full]
+    if not lib.h3_gpu_vsa_bf16(whole, env.wrap(whole_out), *ins):
+        raise RuntimeError(gpu.error())
     torch.cuda.synchronize()
-    dist.barrier()
+    mine = gpu_tensor_view(torch, slots[4], gpu, rows, HEADS)[:plan.valid_rows(rank)]
+    same = bool(torch.equal(mine.view(torch.int16),
+                            whole_out[rank * rows:rank * rows + plan.valid_rows(rank)].view(torch.int16)))
+    if world > 1:
+        flag = torch.tensor([0 if same else 1], device=device)
+        env.dist.all_reduce(flag)
+        same = int(flag.item()) == 0
+    lib.h3_gpu_vsa_free(whole)
     lib.h3_gpu_vsa_free(vsa)
-    for t in slots:
-        lib.h3_gpu_tensor_free(t)
-    lib.h3b_exchange_free(xh)
-    return {"workload": "video sparse attention step at %d GPUs: 4 fused scatters, VSA on %d heads over %d rows "
-                        "(%d tiles, keep 12.5 %%), fused gather" % (world, hg, sequence, tiles),
-            "ms_per_step": ms, "n_gpus": world, "steps": steps}
+    env.free_exchange(exchange, slots)
+    if not same:
+        raise SystemExit("video sparse attention over head shards differs from the one-GPU result")
+    return {"workload": "video sparse attention step at %d GPUs: one fused scatter of q, k, v, gate; VSA on %d heads "
+                        "over %d rows (%d tiles, keep 12.5 %%); fused gather" % (world, hg, sequence, tiles),
+            "ms_per_step": ms, "n_gpus": world, "steps": steps,
+            "parity": {"bit_identical_to_one_gpu_all_heads": same, "ranks": world}}
+
+
+def run_comparators():
+    """Same-box context for the dense number, reported only: the attention kernels that ship in
+    this image - torch scaled_dot_product_attention (flash, cuDNN and memory-efficient back ends)
+    and the flash_attn wheel - on the benchmark shape (L=52,352, H=24, D=128, bf16, no mask).
+    None of them is the reference (which has no Blackwell attention kernel) and none is used by
+    this library. Runs in a process of its own: whatever a third-party kernel does stays there."""
+    import torch
+    import torch.nn.functional as F
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    g = torch.Generator(device=device)
+    g.manual_seed(1002)
+    q, k, v = (torch.randn(SEQ, HEADS, DIM, generator=g, device=device).to(torch.bfloat16) for _ in range(3))
+    flops = 4.0 * SEQ * SEQ * HEADS * DIM
+    out = {"workload": "L=%d, H=%d, D=%d bf16, inputs resident, 10 timed calls after 3 warm-ups (as the main loop)" % (SEQ, HEADS, DIM)}
+
+    def measure(name, fn):
+        try:
+            fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(10):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / 10
+            out[name] = {"ms": ms, "tflops": flops / ms / 1e9}
+        except Exception as e:   # a back end that does not support this GPU or shape
+            out[name] = {"unavailable": (type(e).__name__ + ": " + str(e))[:160]}
+
+    try:
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        # [1, H, L, D] views of the token-major tensors
+        qt, kt, vt = (x.permute(1, 0, 2).unsqueeze(0) for x in (q, k, v))
+        for name, backend in (("torch_sdpa_flash", SDPBackend.FLASH_ATTENTION),
+                              ("torch_sdpa_cudnn", SDPBackend.CUDNN_ATTENTION),
+                              ("torch_sdpa_efficient", SDPBackend.EFFICIENT_ATTENTION)):
+            def call(backend=backend):
+                with sdpa_kernel(backend):
+                    return F.scaled_dot_product_attention(qt, kt, vt, scale=SCALE)
+            measure(name, call)
+    except Exception as e:
+        out["torch_sdpa"] = {"unavailable": str(e)[:160]}
+    try:
+        from flash_attn import flash_attn_func
+        measure("flash_attn_wheel", lambda: flash_attn_func(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0),
+                                                            softmax_scale=SCALE))
+    except Exception as e:
+        out["flash_attn_wheel"] = {"unavailable": (type(e).__name__ + ": " + str(e))[:160]}
+    print(json.dumps(out), flush=True)
+
+
+def comparators_in_child():
+    try:
+        r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--workload", "comparators"],
+                           capture_output=True, text=True, timeout=400)
+        lines = [x for x in r.stdout.splitlines() if x.startswith("{")]
+        return json.loads(lines[-1]) if lines else {"unavailable": (r.stderr or "no output")[-200:]}
+    except Exception as e:
+        return {"unavailable": str(e)[:200]}
 
 
 def secondary(gpu, torch, device, stream, pk, only=None, steps=5):
@@ -642,6 +934,45 @@ def vsa_part(gpu, torch, device, pk, out, events, wrap, g):
     fine_ms = events(fine_only)
     pairs = (tiles - prefix) * (prefix + keep) + prefix * tiles
     fine_flops = pairs * 4.0 * 64 * 64 * 128 * HEADS
+    # The pair-walk kernel (mode 1) on the same lists, and how much MMA work each kernel executes
+    # per selected (query tile, KV tile) pair: the pair walk multiplies both halves of a pair of
+    # adjacent query tiles by every tile of the UNION of their lists; the persistent kernel only
+    # pads an odd list to a whole step.
+    counts = gpu.read_device(d(vsa, 10), (HEADS, tiles), np.int32).astype(np.int64)
+    indices = gpu.read_device(d(vsa, 9), (HEADS, tiles, tiles), np.int32)
+    selected = int(counts.sum())
+    steps_t = int(((counts + 1) // 2).sum()) * 2
+    union = 0
+    for h in range(0, HEADS, 8):          # a sample of the heads is enough for the ratio
+        for a in range(0, tiles - 1, 2):
+            la, lb = indices[h, a, :counts[h, a]], indices[h, a + 1, :counts[h, a + 1]]
+            union += 2 * len(np.union1d(la, lb))
+    union_selected = int(counts[0:HEADS:8, :tiles - tiles % 2].sum())
+    lib.h3b_vsa_fine_mode(1)
+    pair_walk_ms = events(fine_only)
+    lib.h3b_vsa_fine_mode(3)
+    persistent_ms = events(fine_only)
+    lib.h3b_vsa_fine_mode(0)
+    # a locality-structured input: every query cube takes the `keep` video cubes nearest to it in
+    # raster order, so neighbouring cubes share most of their lists (what real activations tend to)
+    near = indices.copy()
+    for qt in range(prefix, tiles):
+        lo = min(max(prefix, qt - keep // 2), tiles - keep)
+        near[:, qt, :prefix + keep] = np.concatenate([np.arange(prefix), np.arange(lo, lo + keep)])
+    t_near = gpu.tensor(near)
+    dn = lib.h3b_tensor_data(t_near)
+
+    def fine_near():
+        gpu.raw("h3_vsa_hopper", d(vsa, 5), d(vsa, 2), d(vsa, 3), d(vsa, 4), None, dn, d(vsa, 10), d(vsa, 1), tiles,
+                HEADS, st)
+
+    near_ms = events(fine_near)
+    lib.h3b_vsa_fine_mode(1)
+    near_pair_ms = events(fine_near)
+    lib.h3b_vsa_fine_mode(3)
+    near_persistent_ms = events(fine_near)
+    lib.h3b_vsa_fine_mode(0)
+    gpu.free(t_near)
     dense_equiv = 4.0 * (tiles * 64) ** 2 * HEADS * DIM
     out["vsa"] = {
         "workload": "text 64 + audio 512 + video 32x30x54, %d tiles (%d prefix), keep %d of %d video tiles, H=%d"
@@ -654,6 +985,21 @@ def vsa_part(gpu, torch, device, pk, out, events, wrap, g):
         "pool_gbs": pool_bytes / pool_ms / 1e6, "pool_frac_of_hbm": pool_bytes / pool_ms / 1e6 / pk["hbm_gbs"],
         "merge_gbs": merge_bytes / merge_ms / 1e6, "merge_frac_of_hbm": merge_bytes / merge_ms / 1e6 / pk["hbm_gbs"],
         "fine_tflops_selected_in_pipeline": fine_flops / fine_in_pipeline_ms / 1e9,
+        "mma_waste": steps_t / selected, "mma_waste_pair_walk": union / union_selected,
+        "fine_ms_pair_walk": pair_walk_ms,
+        "fine_frac_of_peak_pair_walk": fine_flops / pair_walk_ms / 1e9 / pk["tflops"],
+        "fine_ms_persistent_only": persistent_ms,
+        "fine_frac_of_peak_persistent_only": fine_flops / persistent_ms / 1e9 / pk["tflops"],
+        # every query cube keeps the video cubes nearest to it: neighbouring lists mostly coincide
+        "clustered_lists": {"fine_ms": near_ms, "fine_frac_of_peak": fine_flops / near_ms / 1e9 / pk["tflops"],
+                            "fine_ms_pair_walk": near_pair_ms,
+                            "fine_frac_of_peak_pair_walk": fine_flops / near_pair_ms / 1e9 / pk["tflops"],
+                            "fine_ms_persistent_only": near_persistent_ms,
+                            "fine_frac_of_peak_persistent_only": fine_flops / near_persistent_ms / 1e9 / pk["tflops"]},
+        # what bounds the persistent kernel: every step moves 176 KB through the SM's shared memory
+        # (64 KB of K/V fills, 96 KB of MMA operand reads, 16 KB of P stores) for 2 selected pairs
+        "fine_smem_bytes_per_step": 176 * 1024,
+        "fine_smem_gbs_per_sm": (steps_t // 2) * 176 * 1024 / 148 / fine_ms / 1e6,
         "note": "fine_ms_alone: fine stage alone in a back-to-back loop (power-capped); stages_ms: CUDA events "
                 "inside one pipeline call; pool/merge rates use the bytes the data flow really moves",
     }
@@ -730,6 +1076,12 @@ def live_part(gpu, torch, device, out, events, wrap, g):
         nk = nq + min(s, 4) * nq
         ms = events(lambda: gpu.call("cross_attention_bf16", to, 0, tq, 0, tk, tv, 0, nq, nk, HEADS), 3, 1)
         steps.append({"step": s, "key_rows": nk, "ms": ms, "tflops": 4.0 * nq * nk * HEADS * DIM / ms / 1e9})
+    # text rows of the live block attend the whole history too (h3_dit_live.inc:95): a short query
+    # block against 64,800 keys
+    short = {}
+    for nq_short in (64, 256, 512):
+        ms = events(lambda: gpu.call("cross_attention_bf16", to, 0, tq, 0, tk, tv, 0, nq_short, 5 * nq, HEADS), 5, 2)
+        short[str(nq_short)] = {"ms": ms, "tflops": 4.0 * nq_short * 5 * nq * HEADS * DIM / ms / 1e9}
     # steady state (4 history chunks + the current one): the reference's way - concatenate the
     # five K and V ranges with device copies, then attend - against the segmented call
     kc, vc = torch.empty_like(k), torch.empty_like(v)
@@ -754,6 +1106,7 @@ def live_part(gpu, torch, device, out, events, wrap, g):
 
     out["live"] = {"workload": "query chunk 12960 rows, keys 12960 + min(step,4)*12960 history rows, H=%d" % HEADS,
                    "steps": steps, "total_ms": sum(x["ms"] for x in steps),
+                   "short_query_rows_against_64800_keys": short,
                    "steady_state_concat_copies_then_attention_ms": events(concat_then_attend, 3, 1),
                    "steady_state_segmented_call_ms": events(segmented, 3, 1)}
 

@@ -41,16 +41,21 @@ cudaError_t attn_sparse_tc5(void *out, const void *q, const void *k, const void 
                             const int *indices, const int *counts, const int *sizes,
                             unsigned tiles, unsigned heads, cudaStream_t stream);
 
-// The persistent block-sparse kernel with the keys on the MMA's M axis (attn_sparse_t.cu). mq has
-// a 64-row box; `ticket` (one zeroed word) and `redo` ([heads][tiles] bytes) are work memory the
-// caller provides on `stream`; tiles whose row sums left the safe exponent range are marked in redo.
+// The persistent block-sparse kernel with the keys on the MMA's M axis (attn_sparse_t.cu), behind a
+// pre-pass that assigns every pair of adjacent query tiles to it or to the pair-walk kernel.
+// mq has a 64-row box; `ticket` (one zeroed word), `redo` and `elsewhere` ([heads][tiles] bytes
+// each) are work memory the caller provides on `stream`. After the launch redo marks the tiles the
+// pair-walk kernel has to compute: those assigned to it, and those whose row sums left the safe
+// exponent range here. assign: -1 by list overlap, 0 all here, 1 all to the pair walk.
 cudaError_t attn_sparse_t_launch(const ::CUtensorMap_st *mq, const ::CUtensorMap_st *mk,
                                  const ::CUtensorMap_st *mv, void *out, float *lse, const int *indices,
                                  const int *counts, const int *sizes, unsigned tiles, unsigned heads,
-                                 unsigned *ticket, unsigned char *redo, bool force_redo, int *status,
-                                 cudaStream_t stream);
-// 0: persistent kernel, marked tiles recomputed by the pair-walk kernel (default); 1: pair-walk
-// kernel only; 2: persistent kernel with every tile marked (exercises the recomputation).
+                                 unsigned *ticket, unsigned char *redo, unsigned char *elsewhere, int assign,
+                                 bool force_redo, int *status, cudaStream_t stream);
+// 0 (default): pairs of query tiles whose lists mostly coincide go to the pair-walk kernel, the
+// others to the persistent kernel, whose out-of-range tiles are recomputed by the pair walk;
+// 1: pair-walk kernel only; 2: persistent kernel for everything, then every tile recomputed;
+// 3: persistent kernel for everything.
 void attn_sparse_set_mode(int mode);
 
 // Warp-level mma.sync kernel (attn_mma.cu): causal / GQA bf16 D=128 and fp16 D=64.

@@ -76,7 +76,8 @@ struct SparseTParams {
     __nv_bfloat16 *out;
     float *lse;
     unsigned *ticket;          // zero at launch
-    unsigned char *redo;       // [heads][tiles], written for every item
+    unsigned char *redo;       // [heads][tiles], written for every item this kernel computes
+    const unsigned char *elsewhere;   // [heads][tiles]: tiles left to the pair-walk kernel (skipped here)
     int *status;
     int tiles, heads, force_redo;
     float scale_log2;
@@ -239,6 +240,10 @@ attn_sparse_t_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
                 const int head = (int)ticket / p.tiles, qt = (int)ticket % p.tiles;
                 const size_t row = (size_t)head * p.tiles + qt;
+                if (p.elsewhere[row]) {   // this tile's pair goes to the pair-walk kernel
+                    i--;
+                    continue;
+                }
                 int count = p.counts[row];
                 bool bad = count < 0 || count > p.tiles;
                 count = max(0, min(count, p.tiles));
@@ -639,6 +644,48 @@ attn_sparse_t_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
 }
 
+// Which kernel takes which pair of adjacent query tiles. The pair-walk kernel multiplies both
+// tiles by every KV tile of the UNION of their lists with M = 128 MMAs that read less shared
+// memory per multiply-add; this kernel multiplies each tile by its own list only. Measured cost:
+// about 990 cycles per union tile there, 692 cycles per list entry here, so a pair goes to the
+// pair walk when |A u B| < 0.7 (|A| + |B|) - lists that mostly coincide, as neighbouring cubes of
+// real video tend to produce - and stays here otherwise. One warp per pair; both lists ascending.
+__global__ void __launch_bounds__(256)
+pair_choice_kernel(const int *__restrict__ indices, const int *__restrict__ counts, unsigned char *elsewhere,
+                   unsigned char *redo, int tiles, int heads, int force) {
+    __shared__ uint32_t bits[8][128];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pairs = (tiles + 1) / 2;
+    const int pair = blockIdx.x * 8 + warp, head = blockIdx.y;
+    if (pair >= pairs) return;
+    const int qa = 2 * pair, qb = qa + 1;
+    const size_t row = (size_t)head * tiles + qa;
+    int choice = 0;
+    if (force >= 0) {
+        choice = force;
+    } else if (qb < tiles) {
+        const int na = max(0, min(counts[row], tiles)), nb = max(0, min(counts[row + 1], tiles));
+        for (int w = lane; w < 128; w += 32) bits[warp][w] = 0u;
+        __syncwarp();
+        for (int i = lane; i < na; i += 32) {
+            const int kt = indices[row * tiles + i];
+            if (kt >= 0 && kt < tiles) atomicOr(&bits[warp][kt >> 5], 1u << (kt & 31));
+        }
+        __syncwarp();
+        int common = 0;
+        for (int i = lane; i < nb; i += 32) {
+            const int kt = indices[(row + 1) * tiles + i];
+            if (kt >= 0 && kt < tiles) common += (bits[warp][kt >> 5] >> (kt & 31)) & 1u;
+        }
+        common = __reduce_add_sync(0xffffffffu, common);
+        choice = 10 * (na + nb - common) < 7 * (na + nb) ? 1 : 0;
+    }
+    if (lane == 0) {
+        elsewhere[row] = redo[row] = (unsigned char)choice;
+        if (qb < tiles) elsewhere[row + 1] = redo[row + 1] = (unsigned char)choice;
+    }
+}
+
 }  // namespace
 
 #ifdef H3B_TRACE
@@ -650,7 +697,8 @@ extern "C" cudaError_t h3b_debug_sparse_trace(long long *host64) {
 cudaError_t attn_sparse_t_launch(const CUtensorMap_st *mq, const CUtensorMap_st *mk, const CUtensorMap_st *mv,
                                  void *out, float *lse, const int *indices, const int *counts, const int *sizes,
                                  unsigned tiles, unsigned heads, unsigned *ticket, unsigned char *redo,
-                                 bool force_redo, int *status, cudaStream_t stream) {
+                                 unsigned char *elsewhere, int assign, bool force_redo, int *status,
+                                 cudaStream_t stream) {
     static thread_local int configured_device = -1, sms = 0;
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
@@ -669,11 +717,16 @@ cudaError_t attn_sparse_t_launch(const CUtensorMap_st *mq, const CUtensorMap_st 
     p.lse = lse;
     p.ticket = ticket;
     p.redo = redo;
+    p.elsewhere = elsewhere;
     p.status = status;
     p.tiles = (int)tiles;
     p.heads = (int)heads;
     p.force_redo = force_redo ? 1 : 0;
     p.scale_log2 = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128), fixed by the reference kernel
+    // assign: -1 = by list overlap, 0 = every pair to this kernel, 1 = every pair to the pair walk
+    pair_choice_kernel<<<dim3(((tiles + 1) / 2 + 7) / 8, heads), 256, 0, stream>>>(indices, counts, elsewhere, redo,
+                                                                                  (int)tiles, (int)heads, assign);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
     const unsigned items = tiles * heads;
     const unsigned grid = items < (unsigned)sms ? items : (unsigned)sms;   // one persistent CTA per SM
     attn_sparse_t_kernel<<<grid, ST_THREADS, ST_SMEM, stream>>>(*mq, *mk, *mv, p);

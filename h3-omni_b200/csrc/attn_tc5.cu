@@ -585,14 +585,16 @@ cudaError_t attn_sparse_tc5(void *out, const void *q, const void *k, const void 
     if (mode == 1) return launch<64, true>(mq, mk, mv, p, grid, stream);
     // Work memory of the persistent kernel, stream-ordered like the logsumexp buffer the
     // reference's wrapper allocates per call (cuda/h3_gpu_cuda.cu:1115-1127): one ticket word
-    // and one mark per query tile.
+    // and two marks per query tile.
     unsigned char *work = nullptr;
-    const size_t work_bytes = 256 + (size_t)tiles * heads;
+    const size_t marks = ((size_t)tiles * heads + 255) / 256 * 256;
+    const size_t work_bytes = 256 + 2 * marks;
     if ((e = cudaMallocAsync(reinterpret_cast<void **>(&work), work_bytes, stream)) != cudaSuccess) return e;
     e = cudaMemsetAsync(work, 0, 256, stream);
     if (e == cudaSuccess)
         e = attn_sparse_t_launch(&mq64, &mk, &mv, out, lse, indices, counts, sizes, tiles, heads,
-                                 reinterpret_cast<unsigned *>(work), work + 256, mode == 2, status, stream);
+                                 reinterpret_cast<unsigned *>(work), work + 256, work + 256 + marks,
+                                 mode == 0 ? -1 : 0, mode == 2, status, stream);
     if (e == cudaSuccess) {
         // marked tiles (row sums outside the safe exponent range) are recomputed with per-row maxima
         p.redo = work + 256;

@@ -133,7 +133,7 @@ extern "C" cudaError_t h3_vsa_hopper(void *out, const void *q, const void *k, co
     return h3b::attn_sparse_tc5(out, q, k, v, lse, indices, counts, sizes, tiles, heads, stream);
 }
 
-extern "C" void h3b_vsa_fine_mode(int mode) { h3b::attn_sparse_set_mode(mode < 0 || mode > 2 ? 0 : mode); }
+extern "C" void h3b_vsa_fine_mode(int mode) { h3b::attn_sparse_set_mode(mode < 0 || mode > 3 ? 0 : mode); }
 
 extern "C" cudaError_t h3b_device_status(int *status, int reset) {
     if (!status) return cudaErrorInvalidValue;

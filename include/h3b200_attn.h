@@ -347,10 +347,14 @@ int h3b_vsa_qkv_rope_bf16(h3_gpu_vsa *vsa, h3_gpu_tensor *output, const h3_gpu_t
                           const h3_gpu_tensor *gate, uint32_t rope_half, float epsilon, int grouped);
 
 /* Which kernel runs the block-sparse fine stage behind h3_vsa_hopper (process-wide; for A/B
- * measurement and tests). 0 (default): the persistent kernel that walks each query tile's own
- * list, with the rare tiles whose softmax sums leave the safe exponent range recomputed by the
- * pair-walk kernel; 1: the pair-walk kernel only (two adjacent query tiles per CTA walk the
- * union of their lists, per-row online softmax); 2: as 0 with every tile recomputed. */
+ * measurement and tests). There are two: the persistent kernel, in which every query tile walks
+ * its own list only, and the pair-walk kernel, in which a CTA takes two adjacent query tiles and
+ * walks the union of their lists (per-row online softmax; cheaper per multiply-add, wasteful when
+ * the two lists differ). 0 (default): a pre-pass gives every pair of tiles to the pair walk when
+ * their lists mostly coincide (|A u B| < 0.7 (|A| + |B|)) and to the persistent kernel otherwise;
+ * the rare tiles whose softmax sums leave the exponent range the persistent kernel covers are
+ * recomputed by the pair walk. 1: pair-walk kernel only. 2: persistent kernel, then every tile
+ * recomputed by the pair walk. 3: persistent kernel for every pair. */
 void h3b_vsa_fine_mode(int mode);
 
 /* Top-k tile selection of video sparse attention with no device allocation at all. It has no

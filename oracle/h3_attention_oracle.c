@@ -676,6 +676,26 @@ ORACLE_API void oracle_ulysses(uint16_t *out, const uint16_t *in, int ranks, int
 /* ---- timed CPU baseline ----------------------------------------------------- */
 
 #include <time.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* Thread count of the OpenMP loops above, for the benchmark's CPU-baseline legs: a launcher may
+ * have exported OMP_NUM_THREADS=1 to its children, so the count is set and read back explicitly. */
+ORACLE_API void oracle_set_threads(int threads) {
+#ifdef _OPENMP
+    if (threads > 0) omp_set_num_threads(threads);
+#else
+    (void)threads;
+#endif
+}
+ORACLE_API int oracle_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
 /*
  * Times oracle_attention (bf16 in, bf16 out) on `threads` OpenMP threads and
  * returns seconds for one pass; used only by the benchmark's cpu_baseline leg.

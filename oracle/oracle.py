@@ -218,6 +218,16 @@ def ulysses(x, inverse=False):
     return out
 
 
+def set_threads(threads):
+    """Use `threads` OpenMP threads from now on; returns the count in effect."""
+    lib().oracle_set_threads(int(threads))
+    return int(lib().oracle_threads())
+
+
+def threads():
+    return int(lib().oracle_threads())
+
+
 def time_attention(q, k, v, scale):
     """Seconds for one bf16 dense attention pass on all OpenMP threads. q: [Lq,H,D]."""
     q, k, v = _c(q, k, v)

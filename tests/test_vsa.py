@@ -211,8 +211,35 @@ def _random_lists(rng, tiles, heads, low=1):
     return indices, counts
 
 
+def test_vsa_fine_pairs_go_to_the_cheaper_kernel(gpu, oracle):
+    """Default mode: pairs of adjacent query tiles with (nearly) the same list are computed by the
+    pair-walk kernel, pairs with different lists by the persistent kernel. With identical lists in
+    every pair the result is the pair-walk kernel's bit for bit; with disjoint lists the
+    persistent kernel's."""
+    tiles, heads = 16, 2
+    sizes = np.full(tiles, 64, dtype=np.int32)
+    q, k, v = (oracle.normal_bf16((heads, tiles * 64, 128), 40 + i) for i in range(3))
+    same = np.zeros((heads, tiles, tiles), dtype=np.int32)
+    apart = np.zeros((heads, tiles, tiles), dtype=np.int32)
+    counts = np.full((heads, tiles), 6, dtype=np.int32)
+    for t in range(tiles):
+        same[:, t, :6] = np.arange(6) + 2 * (t // 2) % 8            # both tiles of a pair: one list
+        apart[:, t, :6] = np.arange(6) * 2 + (t & 1)                  # even tiles / odd tiles: disjoint
+    try:
+        for lists, twin in ((same, 1), (apart, 3)):
+            got = {}
+            for mode in (0, twin):
+                gpu.lib.h3b_vsa_fine_mode(mode)
+                got[mode], _ = _fine_direct(gpu, q, k, v, lists, counts, sizes)
+            assert np.array_equal(got[0], got[twin])
+            _, want, _ = oracle.vsa_fine(q, k, v, lists, counts, sizes)
+            assert np.abs(oracle.from_bf16(got[0]) - want).max() <= 1e-2
+    finally:
+        gpu.lib.h3b_vsa_fine_mode(0)
+
+
 def test_vsa_fine_kernels_agree(gpu, oracle):
-    """The three fine-stage modes on the same lists (odd and even list lengths, partial tiles):
+    """The fine-stage modes on the same lists (odd and even list lengths, partial tiles):
     the persistent kernel and the pair-walk kernel both meet the oracle; with every tile marked
     for recomputation the result is the pair-walk kernel's, bit for bit."""
     rng = np.random.default_rng(21)
@@ -224,7 +251,7 @@ def test_vsa_fine_kernels_agree(gpu, oracle):
     _, want, want_lse = oracle.vsa_fine(q, k, v, indices, counts, sizes)
     got = {}
     try:
-        for mode in (0, 1, 2):
+        for mode in (0, 1, 2, 3):
             gpu.lib.h3b_vsa_fine_mode(mode)
             bits, lse = _fine_direct(gpu, q, k, v, indices, counts, sizes, want_lse=True)
             out = oracle.from_bf16(bits)
