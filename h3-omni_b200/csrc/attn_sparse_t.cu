@@ -615,7 +615,11 @@ attn_sparse_t_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     ee[x] = (u1 ? hi : lo) + __shfl_xor_sync(0xffffffffu, u1 ? lo : hi, 1);
                 }
                 const int col = (u16 ? 32 : 0) + (u8 ? 16 : 0) + (u4 ? 8 : 0) + (u2 ? 4 : 0) + (u1 ? 2 : 0);
-                float *mine = lpart + (b * 8 + warp) * 64;
+                // The partial sums are filed by the parity of the item's OWN step numbers (this group
+                // took the even or the odd ones), not by the group's number: which group gets an
+                // item's first step depends on what the CTA computed before, and the epilogue's
+                // summation order - hence the result's last bit - must not.
+                float *mine = lpart + (b * 8 + ((k ^ (G & 1)) * 4 + (warp & 3))) * 64;
                 mine[col] = ee[0];
                 mine[col + 1] = ee[1];
 #pragma unroll

@@ -131,6 +131,32 @@ def test_vsa_keep_override_and_ties(gpu, oracle):
         vsa.close()
 
 
+def test_vsa_head_split_is_bit_exact(gpu, oracle):
+    """Heads are independent: the same call on a subset of the heads gives the same bits for those
+    heads (the property the reference checks for its head-sharded attention,
+    tests/live/sharding.py:38-46). The persistent fine-stage kernel hands query tiles to CTAs
+    dynamically, so this also pins that a tile's result does not depend on what its CTA computed
+    before it."""
+    text, audio, shape, heads = 64, 64, (16, 16, 32), 6
+    whole = Vsa(gpu, text, audio, shape, heads)
+    part = Vsa(gpu, text, audio, shape, 3)
+    try:
+        q, k, v, gate = inputs(oracle, whole.rows, heads, 2024, 0.3)
+        for mode in (0, 3):
+            gpu.lib.h3b_vsa_fine_mode(mode)
+            all_heads = whole.run(q, k, v, gate)
+            for lo in (0, 3):
+                some = part.run(*[np.ascontiguousarray(a[:, lo:lo + 3]) for a in (q, k, v, gate)])
+                assert np.array_equal(some, all_heads[:, lo:lo + 3]), (mode, lo)
+            again = whole.run(q, k, v, gate)
+            assert np.array_equal(again, all_heads), mode
+        assert gpu.device_status() == 0
+    finally:
+        gpu.lib.h3b_vsa_fine_mode(0)
+        whole.close()
+        part.close()
+
+
 def test_vsa_block_softmax_order_2051_tiles(gpu, oracle):
     """Above 2048 tiles the pooled softmax uses the 1024-thread reduction order
     (reference cuda/vsa.cuh:108-156; case (3, 11, (4, 4, 8193), 1) of tests/fasth3/vsa.py:112)."""
