@@ -23,14 +23,17 @@ OUT = HERE / "_ref" / "libh3_ref_cuda.so"
 PRODUCT = ROOT / "h3-omni_b200" / "libh3b200_attn.so"
 
 
-def reference_root():
-    return Path(os.environ.get("H3_REF_ROOT", "/root/reference"))
+def reference_root(argument=None):
+    """The reference tree: the argument, else H3_REF_ROOT; None when neither is given."""
+    root = argument or os.environ.get("H3_REF_ROOT")
+    return Path(root) if root else None
 
 
-def build_if_possible(force=False):
+def build_if_possible(root=None, force=False):
     """Returns the library path, or None when the reference tree or nvcc is not available
     (on the GPU box the prebuilt file travels with the repository instead)."""
-    source = reference_root() / "cuda" / "h3_gpu_cuda.cu"
+    ref = reference_root(root)
+    source = ref / "cuda" / "h3_gpu_cuda.cu" if ref else Path("/nonexistent")
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not source.exists() or not Path(nvcc).exists() or not PRODUCT.exists():
         return OUT if OUT.exists() else None
@@ -38,7 +41,6 @@ def build_if_possible(force=False):
                                                                   PRODUCT.stat().st_mtime):
         return OUT
     OUT.parent.mkdir(exist_ok=True)
-    ref = reference_root()
     cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", "--fmad=false", "-w", "-DH3_VSA",
            "-Xcompiler", "-fPIC", "-shared", "-o", str(OUT), str(source), "-I", str(ref),
            "-I", str(ref / "cuda"), "-L", str(PRODUCT.parent), "-lh3b200_attn", "-lcublas",
@@ -51,4 +53,5 @@ def build_if_possible(force=False):
 
 
 if __name__ == "__main__":
-    print(build_if_possible(force=True))
+    import sys
+    print(build_if_possible(sys.argv[1] if len(sys.argv) > 1 else None, force=True))

@@ -6,13 +6,15 @@ from pathlib import Path
 import numpy as np
 
 REF_LIB = Path(__file__).resolve().parents[1] / "oracle" / "_ref" / "libh3_ref_cuda.so"
+# the same backend with its attention stages replaced by this library's (h3-omni_b200/glue_build.py)
+GLUE_LIB = Path(__file__).resolve().parents[1] / "h3-omni_b200" / "libh3_cuda_b200.so"
 
 
 class Reference:
     """Minimal ctypes driver of the reference backend (its public h3_gpu.h / h3_cuda.h calls)."""
 
-    def __init__(self):
-        self.lib = C.CDLL(str(REF_LIB))
+    def __init__(self, library=REF_LIB):
+        self.lib = C.CDLL(str(library))
         L = self.lib
         for name in ("h3_gpu_create", "h3_gpu_tensor_from_bf16", "h3_gpu_tensor_from_f32",
                      "h3_gpu_tensor_new_bf16", "h3_gpu_tensor_new_f32", "h3_gpu_vsa_new", "h3_gpu_error"):
