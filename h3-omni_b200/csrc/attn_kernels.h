@@ -30,7 +30,12 @@ cudaError_t attn_dense_tc5_pair(const ::CUtensorMap_st *mq, const ::CUtensorMap_
                                 unsigned lq, unsigned lk, unsigned heads, unsigned kv_heads,
                                 float scale, int *status, cudaStream_t stream,
                                 const PeerOutput *peer = nullptr, unsigned segments = 0,
-                                const unsigned *segment_rows = nullptr);
+                                const unsigned *segment_rows = nullptr, unsigned split_tiles = 0);
+// Split-KV (batch 1): with split_tiles > 0 the launch above cuts the keys into slices of
+// split_tiles 128-row tiles on grid.z and writes per-slice outputs [slices][lq][heads][128] bf16 and
+// logsumexp [slices][heads][lq] f32 (both required); this combines them.
+cudaError_t attn_merge_splits(void *out, float *lse_out, const void *partial, const float *lse, unsigned splits,
+                              unsigned lq, unsigned heads, cudaStream_t stream);
 // Rectangular attention of lq query rows against the concatenation of `segments` (<= 6) K/V row
 // ranges, each token-major [rows_s][heads][128], without concatenating them (batch 1).
 cudaError_t attn_segments_tc5(void *out, const void *q, const void *const *k, const void *const *v,

@@ -21,6 +21,8 @@
 //   fwd_attend_ker<128> (cuda/vendor/vsa_hopper_forward.cuh:68-270) behind h3_vsa_hopper.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "attn_kernels.h"
 #include "sm100_ptx.cuh"
 #include "softmax_tc5.cuh"
@@ -514,6 +516,38 @@ cudaError_t attn_dense_tc5(void *out, const void *q, const void *k, const void *
     p.out = static_cast<__nv_bfloat16 *>(out);
     p.lse = lse;
     p.status = status;
+    // A short query block against a long key range (live mode: the text rows of a chunk against
+    // the whole KV history, h3_dit_live.inc:95) gives far fewer CTAs than the GPU has SMs, each
+    // walking every key. Then the keys are cut into slices that run side by side and a small
+    // kernel merges the slices by their logsumexp.
+    if (!peer && batch == 1) {
+        static thread_local int sms_device = -1, sms = 0;
+        int device = 0;
+        if ((e = cudaGetDevice(&device)) != cudaSuccess) return e;
+        if (device != sms_device) {
+            if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return e;
+            sms_device = device;
+        }
+        const unsigned ctas = ((lq + 2 * BM - 1) / (2 * BM)) * heads, key_tiles = (lk + 127) / 128;
+        if (ctas * 2 <= (unsigned)sms && key_tiles >= 32) {
+            unsigned splits = std::min<unsigned>({16u, (unsigned)sms / ctas, key_tiles / 8});
+            const unsigned split_tiles = (key_tiles + splits - 1) / splits;
+            splits = (key_tiles + split_tiles - 1) / split_tiles;
+            if (splits >= 2) {
+                // work memory, stream-ordered like the logsumexp buffer of the reference's wrapper
+                const size_t part_bytes = (size_t)splits * lq * heads * 256, lse_bytes = (size_t)splits * heads * lq * 4;
+                char *work = nullptr;
+                if ((e = cudaMallocAsync(reinterpret_cast<void **>(&work), part_bytes + lse_bytes, stream)) != cudaSuccess)
+                    return e;
+                float *part_lse = reinterpret_cast<float *>(work + part_bytes);
+                e = attn_dense_tc5_pair(&mq, &mk, &mv, work, part_lse, 1, lq, lk, heads, kv_heads, scale, status,
+                                        stream, nullptr, 0, nullptr, split_tiles);
+                if (e == cudaSuccess) e = attn_merge_splits(out, lse, work, part_lse, splits, lq, heads, stream);
+                const cudaError_t freed = cudaFreeAsync(work, stream);
+                return e != cudaSuccess ? e : freed;
+            }
+        }
+    }
     // More than one query tile: the two-tile-per-CTA kernel (attn_tc5_pair.cu).
     if (lq > (unsigned)BM || peer)
         return attn_dense_tc5_pair(&mq, &mk, &mv, out, lse, batch, lq, lk, heads, kv_heads, scale,

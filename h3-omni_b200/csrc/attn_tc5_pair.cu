@@ -57,6 +57,10 @@ struct PairKvMaps {
 struct PairParams {
     int segments, seg_rows[PAIR_MAX_SEGMENTS];
     int lq, lk, heads, kv_heads;
+    // Split-KV for short query blocks: when split_tiles > 0, blockIdx.z is not a batch but a
+    // slice of split_tiles key tiles; the CTA writes its partial output and logsumexp as if
+    // they were batch element blockIdx.z, and merge_splits_kernel combines the slices.
+    int split_tiles;
     float scale, scale_log2;
     __nv_bfloat16 *out;
     float *lse;
@@ -88,11 +92,15 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     auto bar_p_full = [&](int t) { return bar0 + 8u * (1 + 2 * ST + 2 + t); };
     auto bar_pv_done = [&](int t) { return bar0 + 8u * (1 + 2 * ST + 4 + t); };
 
-    const int head = blockIdx.y, batch = blockIdx.z;
+    const int head = blockIdx.y, batch = p.split_tiles ? 0 : blockIdx.z, out_batch = blockIdx.z;
     const int kv_head = head / (p.heads / p.kv_heads);
     const int q_row0 = blockIdx.x * 2 * PBM;
+    const int tile0 = p.split_tiles * (int)blockIdx.z;   // first key tile of this CTA's slice (0 without split)
+    // key rows of range s as this CTA sees it (a split call has one range and takes a slice of it)
+    const int slice_rows = p.split_tiles ? min(p.seg_rows[0] - tile0 * PBN, p.split_tiles * PBN) : 0;
+    auto seg_rows = [&](int s) { return p.split_tiles ? slice_rows : p.seg_rows[s]; };
     int n_tiles = 0;   // key tiles over all segments
-    for (int s = 0; s < p.segments; s++) n_tiles += (p.seg_rows[s] + PBN - 1) / PBN;
+    for (int s = 0; s < p.segments; s++) n_tiles += (seg_rows(s) + PBN - 1) / PBN;
 
     if (tid == 0) {
         mbar_init(bar_q_full, 1);
@@ -132,7 +140,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             int idx = 0;   // ring position: even = K tile, odd = V tile
             bool ok = true;
             for (int seg = 0; ok && seg < p.segments; seg++) {
-                const int tiles = (p.seg_rows[seg] + PBN - 1) / PBN;
+                const int tiles = (seg_rows(seg) + PBN - 1) / PBN;
                 for (int tile = 0; ok && tile < tiles; tile++) {
                     for (int which = 0; which < 2; which++, idx++) {
                         const int s = idx % ST, use = idx / ST;
@@ -143,8 +151,8 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                         const uint32_t dst = ring + s * PAIR_TILE_BYTES;
                         const void *map = which ? (const void *)&kv.v[seg] : (const void *)&kv.k[seg];
                         mbar_arrive_expect_tx(bar_full(s), PAIR_TILE_BYTES);
-                        tma_load_4d(dst, map, bar_full(s), 0, kv_head, tile * PBN, batch);
-                        tma_load_4d(dst + PAIR_HALF_BYTES, map, bar_full(s), 64, kv_head, tile * PBN, batch);
+                        tma_load_4d(dst, map, bar_full(s), 0, kv_head, (tile0 + tile) * PBN, batch);
+                        tma_load_4d(dst + PAIR_HALF_BYTES, map, bar_full(s), 64, kv_head, (tile0 + tile) * PBN, batch);
                     }
                 }
             }
@@ -272,11 +280,11 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #endif
         int seg = 0, seg_tile = 0;   // which segment, which tile of it, step j is
         for (int j = 0; j < n_tiles; j++) {
-            while (seg_tile * PBN >= p.seg_rows[seg]) {
+            while (seg_tile * PBN >= seg_rows(seg)) {
                 seg++;
                 seg_tile = 0;
             }
-            const int nvalid = min(PBN, p.seg_rows[seg] - seg_tile * PBN);
+            const int nvalid = min(PBN, seg_rows(seg) - seg_tile * PBN);
             seg_tile++;
             {
                 TRACE_T0();
@@ -404,10 +412,10 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 dst = p.peer_out[store ? owner : 0] +
                       ((size_t)local * p.total_heads + (size_t)p.rank * p.heads + head) * PHD;
             } else {
-                dst = p.out + (((size_t)batch * p.lq + row) * p.heads + head) * PHD;
+                dst = p.out + (((size_t)out_batch * p.lq + row) * p.heads + head) * PHD;
             }
             if (store && p.lse)
-                p.lse[((size_t)batch * p.heads + head) * p.lq + row] = m_ref * p.scale + __logf(l);
+                p.lse[((size_t)out_batch * p.heads + head) * p.lq + row] = m_ref * p.scale + __logf(l);
 #pragma unroll
             for (int c = 0; c < PHD / 32; c++) {
                 uint32_t v[32];
@@ -443,13 +451,55 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
 }
 
+// Combines the slices of a split-KV call: out[r][h][:] = sum_s w_s O_s[r][h][:] / sum_s w_s with
+// w_s = exp(lse_s - max_s lse_s). One thread per (row, head, eight dims).
+__global__ void __launch_bounds__(256)
+merge_splits_kernel(__nv_bfloat16 *__restrict__ out, float *__restrict__ lse_out, const uint4 *__restrict__ partial,
+                    const float *__restrict__ lse, int splits, int lq, int heads) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)lq * heads * (PHD / 8);
+    if (i >= total) return;
+    const int v = (int)(i % (PHD / 8)), head = (int)((i / (PHD / 8)) % heads), row = (int)(i / ((size_t)(PHD / 8) * heads));
+    float top = -INFINITY;
+    for (int s = 0; s < splits; s++) top = fmaxf(top, lse[((size_t)s * heads + head) * lq + row]);
+    float acc[8] = {}, weight = 0.0f;
+    for (int s = 0; s < splits; s++) {
+        const float w = __expf(lse[((size_t)s * heads + head) * lq + row] - top);
+        const uint4 x = partial[(((size_t)s * lq + row) * heads + head) * (PHD / 8) + v];
+        const uint32_t words[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            acc[2 * k] = fmaf(w, __uint_as_float(words[k] << 16), acc[2 * k]);
+            acc[2 * k + 1] = fmaf(w, __uint_as_float(words[k] & 0xffff0000u), acc[2 * k + 1]);
+        }
+        weight += w;
+    }
+    const float inv = 1.0f / weight;
+    uint4 y;
+    y.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+    y.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+    y.z = pack_bf16(acc[4] * inv, acc[5] * inv);
+    y.w = pack_bf16(acc[6] * inv, acc[7] * inv);
+    reinterpret_cast<uint4 *>(out)[i] = y;
+    if (lse_out && v == 0) lse_out[(size_t)head * lq + row] = top + __logf(weight);
+}
+
 }  // namespace
+
+cudaError_t attn_merge_splits(void *out, float *lse_out, const void *partial, const float *lse, unsigned splits,
+                              unsigned lq, unsigned heads, cudaStream_t stream) {
+    const size_t total = (size_t)lq * heads * (PHD / 8);
+    merge_splits_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+        static_cast<__nv_bfloat16 *>(out), lse_out, static_cast<const uint4 *>(partial), lse, (int)splits, (int)lq,
+        (int)heads);
+    return cudaGetLastError();
+}
 
 cudaError_t attn_dense_tc5_pair(const CUtensorMap_st *mq, const CUtensorMap_st *mk,
                                 const CUtensorMap_st *mv, void *out, float *lse, unsigned batch,
                                 unsigned lq, unsigned lk, unsigned heads, unsigned kv_heads,
                                 float scale, int *status, cudaStream_t stream, const PeerOutput *peer,
-                                unsigned segments, const unsigned *segment_rows) {
+                                unsigned segments, const unsigned *segment_rows, unsigned split_tiles) {
     static thread_local int configured_device = -1;
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
@@ -462,6 +512,12 @@ cudaError_t attn_dense_tc5_pair(const CUtensorMap_st *mq, const CUtensorMap_st *
     }
     // mk / mv point to `segments` maps each; without a segment list: one range of lk rows
     if (segments > (unsigned)PAIR_MAX_SEGMENTS || (segments > 1 && batch != 1)) return cudaErrorInvalidValue;
+    // split-KV: one key range, batch 1, no peer output; the slices ride on grid.z
+    unsigned splits = 1;
+    if (split_tiles) {
+        if (segments > 1 || batch != 1 || peer || !lse) return cudaErrorInvalidValue;
+        splits = ((lk + PBN - 1) / PBN + split_tiles - 1) / split_tiles;
+    }
     PairKvMaps kv{};
     PairParams p{};
     p.segments = segments ? (int)segments : 1;
@@ -480,6 +536,7 @@ cudaError_t attn_dense_tc5_pair(const CUtensorMap_st *mq, const CUtensorMap_st *
     p.out = static_cast<__nv_bfloat16 *>(out);
     p.lse = lse;
     p.status = status;
+    p.split_tiles = (int)split_tiles;
     if (peer) {
         if (batch != 1 || !peer->rows_per_rank) return cudaErrorInvalidValue;
         for (int i = 0; i < 16; i++) p.peer_out[i] = static_cast<__nv_bfloat16 *>(peer->base[i]);
@@ -487,7 +544,7 @@ cudaError_t attn_dense_tc5_pair(const CUtensorMap_st *mq, const CUtensorMap_st *
         p.rank = peer->rank;
         p.total_heads = peer->total_heads;
     }
-    dim3 grid((lq + 2 * PBM - 1) / (2 * PBM), heads, batch);
+    dim3 grid((lq + 2 * PBM - 1) / (2 * PBM), heads, split_tiles ? splits : batch);
     attn_tc5_pair_kernel<<<grid, PAIR_THREADS, PAIR_SMEM_BYTES, stream>>>(*mq, kv, p);
     return cudaGetLastError();
 }

@@ -42,6 +42,27 @@ def test_sdpa_bf16_larger(gpu, oracle, L, H):
     assert gpu.device_status() == 0
 
 
+@pytest.mark.parametrize("nq,nk,heads", [(64, 9000, 4), (200, 16001, 3), (300, 33000, 2), (1, 5000, 24)])
+def test_short_query_block_against_long_keys_split_kv(gpu, oracle, nq, nk, heads):
+    """Live mode's text rows against the whole KV history (h3_dit_live.inc:95): too few query tiles
+    to fill the GPU, so the keys are cut into slices computed side by side and merged by their
+    logsumexp. Same limits as every dense call, ragged last slice included, and the kernel-adapter
+    symbol's logsumexp output against the FP32 recomputation."""
+    q = oracle.normal_bf16((1, nq, heads, 128), 31)
+    k, v = (oracle.normal_bf16((1, nk, heads, 128), 32 + i) for i in range(2))
+    tq, tk, tv = gpu.tensor(q), gpu.tensor(k), gpu.tensor(v)
+    ty = gpu.tensor(np.full(q.shape, 0x7fc0, dtype=np.uint16))
+    gpu.call("cross_attention_bf16", ty, 0, tq, 0, tk, tv, 0, nq, nk, heads)
+    want, _, want_lse = oracle.attention(q, k, v, SCALE, want_lse=True)
+    assert_attention_close(oracle.from_bf16(gpu.read(ty, q.shape)), want)
+    tl = gpu.tensor(np.zeros((heads, nq), dtype=np.float32))
+    d = gpu.lib.h3b_tensor_data
+    gpu.raw("h3_flash3_cross_bf16", d(ty), d(tq), d(tk), d(tv), d(tl), nq, nk, heads, C.c_float(SCALE),
+            gpu.lib.h3b_gpu_stream(gpu.gpu))
+    assert np.abs(gpu.read(tl, (heads, nq), np.float32) - want_lse.reshape(heads, nq)).max() <= 2e-3
+    assert gpu.device_status() == 0
+
+
 def test_c1_dense_l4096_h8(gpu, oracle):
     """Benchmark configuration 1 exactly: Q, K, V bf16 [1, 8, 4096, 128] from N(0, 1), seed 1001,
     scale 1/sqrt(128), no mask; max-abs <= 1e-2 and cosine >= 0.9999 against the FP32
