@@ -206,6 +206,36 @@ int h3b_cross_attention_segments_bf16(h3_gpu *gpu, h3_gpu_tensor *out, size_t ou
                                       const h3_gpu_tensor *const *values, const size_t *kv_row,
                                       const uint32_t *kv_rows);
 
+/* Live mode's KV history of one layer as a ring buffer (no counterpart as an object in the
+ * reference, which keeps h3_live_kv tensor pairs that it allocates, copies and frees at every
+ * chunk: h3_dit.c:77-80, live_pair_copy, and the commit at h3_dit.c:4451-4481). One allocation at
+ * h3b_live_kv_new holds every slot; afterwards nothing is allocated or freed.
+ *   stage       - the clean chunk's media K/V rows (first audio_rows of them audio) are copied in:
+ *                 live_pair_copy;
+ *   commit      - the staged chunk becomes the newest history chunk and the older of the two recent
+ *                 chunks is dropped, by index rotation; the first commit also keeps the chunk's
+ *                 video rows as the sink (h3_dit.c:4457-4481);
+ *   clear_audio - the recent chunks are attended without their audio rows from now on (:4483-4486);
+ *   attention   - query rows against  text | sink (from the third commit) | older | newer |
+ *                 current media  as K/V row ranges, i.e. the second call of h3_dit_live.inc:95-99
+ *                 without the concatenation copies of :81-94. key / value are the block's own
+ *                 [sequence][heads][128] rows, text rows first. Scale 1/sqrt(128).
+ * chunk_rows: the largest number of media rows a chunk can have. */
+typedef struct h3b_live_kv h3b_live_kv;
+h3b_live_kv *h3b_live_kv_new(h3_gpu *gpu, uint32_t chunk_rows, uint32_t heads);
+void h3b_live_kv_free(h3b_live_kv *history);
+void h3b_live_kv_reset(h3b_live_kv *history);
+uint32_t h3b_live_kv_commits(const h3b_live_kv *history);
+uint32_t h3b_live_kv_history_rows(const h3b_live_kv *history);
+int h3b_live_kv_stage(h3b_live_kv *history, const h3_gpu_tensor *key, const h3_gpu_tensor *value,
+                      size_t first_row, uint32_t rows, uint32_t audio_rows);
+int h3b_live_kv_commit(h3b_live_kv *history);
+int h3b_live_kv_clear_audio(h3b_live_kv *history);
+int h3b_live_kv_attention_bf16(h3b_live_kv *history, h3_gpu_tensor *out, size_t out_row,
+                               const h3_gpu_tensor *q, size_t q_row, uint32_t query_rows,
+                               const h3_gpu_tensor *key, const h3_gpu_tensor *value, uint32_t text_rows,
+                               uint32_t sequence);
+
 /* Dense attention from and to HOST memory, head dim 128: q, k, v, out are token-major
  * [sequence][heads][128] bf16 in host memory (pinned for full speed). The heads are cut into
  * head_groups groups (heads % head_groups == 0) and copy-in, kernel and copy-out of
