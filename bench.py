@@ -157,7 +157,7 @@ def main():
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="dense", choices=["dense", "vsa", "live", "producer", "comparators"])
+    parser.add_argument("--workload", default="dense", choices=["dense", "vsa", "live", "producer", "out_proj", "comparators"])
     parser.add_argument("--no-also", action="store_true", help="skip the secondary measurements")
     parser.add_argument("--exchange", default="push", choices=["push", "nccl"],
                         help="N>1: fused peer-memory exchange kernel (default) or transpose + NCCL send/recv")
@@ -885,7 +885,54 @@ def secondary(gpu, torch, device, stream, pk, only=None, steps=5):
         live_part(gpu, torch, device, out, events, wrap, g)
     if only in (None, "producer"):
         producer_part(gpu, torch, device, pk, out, events, wrap, g)
+    if only in (None, "out_proj"):
+        out_proj_part(gpu, torch, device, pk, out, events, wrap, g)
     return out
+
+
+def out_proj_part(gpu, torch, device, pk, out, events, wrap, g):
+    """What follows attention in a block (h3_dit.c:2573-2597): output projection INNER -> HIDDEN with
+    gate + residual in the GEMM epilogue, then AdaLN; beside it the same arithmetic as separate
+    torch ops (library GEMM + elementwise), for context."""
+    lib = gpu.lib
+    g.manual_seed(1007)
+    rows, inner, hidden, slots = SEQ, HEADS * DIM, 5376, 6
+    x = (0.5 * torch.randn(rows, inner, generator=g, device=device)).to(torch.bfloat16)
+    w = (torch.randn(hidden, inner, generator=g, device=device) / inner ** 0.5).to(torch.bfloat16)
+    residual = torch.randn(rows, hidden, generator=g, device=device).to(torch.bfloat16)
+    norm_w = (1 + 0.1 * torch.randn(hidden, generator=g, device=device)).to(torch.bfloat16)
+    mod = (0.3 * torch.randn(1, slots, hidden, generator=g, device=device)).to(torch.bfloat16)
+    row_map = torch.zeros(rows, dtype=torch.int32, device=device)
+    gated, normed = torch.empty_like(residual), torch.empty_like(residual)
+    t = [wrap(a) for a in (residual, x, w, norm_w, mod, mod)]
+    tmap = gpu.wrap(row_map.data_ptr(), rows, 3)     # U32
+    tg, tn = wrap(gated), wrap(normed)
+
+    def fused():
+        if not lib.h3b_attention_output_gate_adaln_bf16(gpu.gpu, tg, tn, *t, tmap, rows, inner, hidden, slots, 2, 3, 4,
+                                                        C.c_float(1e-5)):
+            raise RuntimeError(gpu.error())
+
+    def gate_only():
+        if not lib.h3b_attention_output_gate_adaln_bf16(gpu.gpu, tg, None, *t, tmap, rows, inner, hidden, slots, 2, 3, 4,
+                                                        C.c_float(1e-5)):
+            raise RuntimeError(gpu.error())
+
+    F = torch.nn.functional
+
+    def separate():
+        y = x @ w.t()
+        r = residual + (y * mod[0, 2]).to(torch.bfloat16)
+        return F.rms_norm(r, (hidden,), norm_w) * (1 + mod[0, 4]) + mod[0, 3]
+
+    flops = 2.0 * rows * inner * hidden
+    fused_ms, gemm_ms, torch_ms = events(fused), events(gate_only), events(separate)
+    out["out_proj"] = {"workload": "rows %d, inner %d -> hidden %d; projection + gate + residual + AdaLN" % (rows, inner, hidden),
+                       "fused_ms": fused_ms, "gemm_with_gate_epilogue_ms": gemm_ms,
+                       "gemm_tflops": flops / gemm_ms / 1e9, "gemm_frac_of_peak": flops / gemm_ms / 1e9 / pk["tflops"],
+                       "adaln_ms": fused_ms - gemm_ms,
+                       "adaln_gbs": 2.0 * rows * hidden * 2 / max(fused_ms - gemm_ms, 1e-6) / 1e6,
+                       "separate_torch_ops_ms": torch_ms}
 
 
 def vsa_part(gpu, torch, device, pk, out, events, wrap, g):

@@ -9,7 +9,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libh3b200_attn.so"
-SOURCES = ["attn_tc5.cu", "attn_sparse_t.cu", "attn_tc5_pair.cu", "attn_mma.cu", "vsa_coarse.cu", "qkv_rope.cu", "ulysses.cu", "h3_gpu_b200.cu", "vsa_object.cu", "multi_gpu.cu", "live_kv.cu"]
+SOURCES = ["attn_tc5.cu", "attn_sparse_t.cu", "attn_tc5_pair.cu", "attn_mma.cu", "vsa_coarse.cu", "qkv_rope.cu", "ulysses.cu", "h3_gpu_b200.cu", "vsa_object.cu", "multi_gpu.cu", "live_kv.cu", "out_proj_gate.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

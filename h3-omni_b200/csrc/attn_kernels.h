@@ -100,6 +100,15 @@ cudaError_t qkv_rope_head_shards(const QkvRopeInput &in, void *const window_q[],
 cudaError_t qkv_rope_vsa_tiles(const QkvRopeInput &in, const int *map, const int *sizes, int tiles,
                                void *const tiled[3], float *const pooled[3], cudaStream_t stream);
 
+// Attention output projection with gate + residual in the GEMM epilogue, and row-wise AdaLN
+// (out_proj_gate.cu). weight [hidden][inner], modulation [mod rows][slots][hidden], all bf16.
+cudaError_t out_proj_gate(void *gated, const void *residual, const void *attention_heads, const void *weight,
+                          const void *modulation, const unsigned *row_map, unsigned rows, unsigned inner,
+                          unsigned hidden, unsigned slots, unsigned gate_slot, cudaStream_t stream);
+cudaError_t adaln_rows(void *output, const void *input, const void *norm_weight, const void *modulation,
+                       const unsigned *row_map, unsigned rows, unsigned width, unsigned slots, unsigned shift_slot,
+                       unsigned scale_slot, float epsilon, cudaStream_t stream);
+
 // Ulysses block transpose (ulysses.cu): out[b][a][:] = in[a][b][:], rows of `row_units` 16-byte units.
 cudaError_t transpose_rows_16b(void *out, const void *in, unsigned a, unsigned b, size_t row_units,
                                cudaStream_t stream);

@@ -416,7 +416,18 @@ cudaError_t vsa_score_select_compress(const float *poolq, const float *poolk, co
         return cudaErrorInvalidValue;
     // 16 query tiles per CTA up to 1400 tiles (two such CTAs share an SM up to about 1130 tiles,
     // one beyond), 8 per CTA beyond that: the score rows of a CTA must fit its shared memory.
-    if (tiles <= 1400)
+    // The kernel is latency-bound (fixed-order fmaf chains, a 32-round threshold search), so its
+    // time is about one CTA's time as long as every CTA is resident: with few heads (a rank's share
+    // under sequence parallelism) 8 tiles per CTA halve that time and still fill the GPU.
+    static thread_local int sms_device = -1, sms = 0;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e == cudaSuccess && device != sms_device) {
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (e == cudaSuccess) sms_device = device;
+    }
+    if (e != cudaSuccess) return e;
+    if (tiles <= 1400 && (size_t)((tiles + 15) / 16) * heads >= (size_t)4 * sms)
         return launch_score_select<2>(poolq, poolk, poolv, scores, indices, counts, compression, tiles,
                                       prefix, keep, heads, scale, stream);
     return launch_score_select<1>(poolq, poolk, poolv, scores, indices, counts, compression, tiles,

@@ -236,6 +236,24 @@ int h3b_live_kv_attention_bf16(h3b_live_kv *history, h3_gpu_tensor *out, size_t 
                                const h3_gpu_tensor *key, const h3_gpu_tensor *value, uint32_t text_rows,
                                uint32_t sequence);
 
+/* What follows attention in every block, as one call (no counterpart as one call in the
+ * reference, which runs h3_gpu_linear_bf16 (INNER -> HIDDEN) and h3_gpu_gate_adaln_bf16,
+ * h3_dit.c:2573-2597, cuda/fast_primitives.cuh:50-124):
+ *   y      = bf16(attention_heads . out_weight^T)      out_weight [hidden][inner], fp32 accumulate
+ *   gated  = bf16(residual + bf16(y * gate_modulation[row_map[row]][gate_slot]))
+ *   output = AdaLN(gated; norm_weight, modulation[row_map[row]][shift_slot / scale_slot], epsilon)
+ * The projection is a tcgen05 GEMM whose epilogue applies gate and residual, so y is never written;
+ * AdaLN follows the reference kernel's operation order (bit-identical to it on the same gated
+ * rows). attention_heads may be an exchange slot (the rows the attention kernel gathered).
+ * gated_residual may alias residual; output == NULL computes the gate only. inner % 64 == 0,
+ * hidden % 8 == 0, hidden <= 8192. */
+int h3b_attention_output_gate_adaln_bf16(
+    h3_gpu *gpu, h3_gpu_tensor *gated_residual, h3_gpu_tensor *output, const h3_gpu_tensor *residual,
+    const h3_gpu_tensor *attention_heads, const h3_gpu_tensor *out_weight, const h3_gpu_tensor *norm_weight,
+    const h3_gpu_tensor *gate_modulation, const h3_gpu_tensor *modulation, const h3_gpu_tensor *row_map,
+    uint32_t rows, uint32_t inner, uint32_t hidden, uint32_t slots, uint32_t gate_slot, uint32_t shift_slot,
+    uint32_t scale_slot, float epsilon);
+
 /* Dense attention from and to HOST memory, head dim 128: q, k, v, out are token-major
  * [sequence][heads][128] bf16 in host memory (pinned for full speed). The heads are cut into
  * head_groups groups (heads % head_groups == 0) and copy-in, kernel and copy-out of

@@ -680,6 +680,69 @@ ORACLE_API void oracle_ulysses(uint16_t *out, const uint16_t *in, int ranks, int
 #include <omp.h>
 #endif
 
+/* Attention output projection, gate and AdaLN: h3_dit.c:2573-2597.
+ *   y = bf16(x . w^T) with FP32 accumulation (cuda/h3_gpu_cuda.cu:774-777; cuBLAS' summation order is
+ *       not knowable, a plain ascending fmaf chain is used), w [hidden][inner];
+ *   gated = bf16(residual + bf16(y * gate)), gate = gate_mod[map[row]][gate_slot]
+ *       (cuda/fast_primitives.cuh:74-90);
+ *   out = bf16(bf16(bf16(gated * inverse * weight) * bf16(1 + scale)) + shift) with the row's sum of
+ *       squares in the kernel's order: thread t < 128 owns the 4-value groups at 4t + 512c, fmaf in
+ *       index order, shuffle-down tree over 32 lanes, warp sums paired 0+2, 1+3, then 0+1
+ *       (cuda/fast_primitives.cuh:64-124). inverse = 1/sqrtf (the GPU uses the approximate rsqrtf). */
+static float adaln_row_sum(const uint16_t *x, unsigned width) {
+    float lane[128];
+    for (unsigned t = 0; t < 128; t++) {
+        float sum = 0.0f;
+        for (unsigned c = 0; 4 * t + 512 * c < width; c++)
+            for (unsigned i = 0; i < 4; i++) {
+                const float v = bf16_to_f32(x[4 * t + 512 * c + i]);
+                sum = fmaf(v, v, sum);
+            }
+        lane[t] = sum;
+    }
+    float warp_sums[4];
+    for (unsigned w = 0; w < 4; w++) {
+        float v[32];
+        for (unsigned l = 0; l < 32; l++) v[l] = lane[32 * w + l];
+        for (unsigned distance = 16; distance; distance >>= 1)
+            for (unsigned l = 0; l < 32; l++)       /* ascending l reads not yet updated partners */
+                v[l] = v[l] + (l + distance < 32 ? v[l + distance] : v[l]);
+        warp_sums[w] = v[0];
+    }
+    warp_sums[0] += warp_sums[2];
+    warp_sums[1] += warp_sums[3];
+    return warp_sums[0] + warp_sums[1];
+}
+ORACLE_API void oracle_out_proj_gate_adaln(uint16_t *gated, uint16_t *out, const uint16_t *residual,
+                                           const uint16_t *x, const uint16_t *w, const uint16_t *norm_weight,
+                                           const uint16_t *gate_mod, const uint16_t *mod, const uint32_t *map,
+                                           unsigned rows, unsigned inner, unsigned hidden, unsigned slots,
+                                           unsigned gate_slot, unsigned shift_slot, unsigned scale_slot,
+                                           float epsilon) {
+#pragma omp parallel for schedule(static)
+    for (long r = 0; r < (long)rows; r++) {
+        const size_t base = (size_t)map[r] * slots * hidden;
+        for (unsigned n = 0; n < hidden; n++) {
+            float acc = 0.0f;
+            for (unsigned k = 0; k < inner; k++)
+                acc = fmaf(bf16_to_f32(x[(size_t)r * inner + k]), bf16_to_f32(w[(size_t)n * inner + k]), acc);
+            const float y = bf16_round(acc);
+            const float g = bf16_to_f32(gate_mod[base + (size_t)gate_slot * hidden + n]);
+            gated[(size_t)r * hidden + n] = f32_to_bf16(bf16_to_f32(residual[(size_t)r * hidden + n]) + bf16_round(y * g));
+        }
+        if (!out) continue;
+        const float total = adaln_row_sum(gated + (size_t)r * hidden, hidden);
+        const float inverse = 1.0f / sqrtf(total / (float)hidden + epsilon);
+        for (unsigned n = 0; n < hidden; n++) {
+            const float xv = bf16_to_f32(gated[(size_t)r * hidden + n]);
+            const float normalized = xv * inverse * bf16_to_f32(norm_weight[n]);
+            const float shift = bf16_to_f32(mod[base + (size_t)shift_slot * hidden + n]);
+            const float scale = bf16_to_f32(mod[base + (size_t)scale_slot * hidden + n]);
+            out[(size_t)r * hidden + n] = f32_to_bf16(bf16_round(bf16_round(normalized) * bf16_round(1.0f + scale)) + shift);
+        }
+    }
+}
+
 /* Thread count of the OpenMP loops above, for the benchmark's CPU-baseline legs: a launcher may
  * have exported OMP_NUM_THREADS=1 to its children, so the count is set and read back explicitly. */
 ORACLE_API void oracle_set_threads(int threads) {

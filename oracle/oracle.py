@@ -218,6 +218,22 @@ def ulysses(x, inverse=False):
     return out
 
 
+def out_proj_gate_adaln(residual, x, w, norm_weight, gate_mod, mod, row_map, slots, gate_slot, shift_slot,
+                        scale_slot, epsilon=1e-5, adaln=True):
+    """x [rows, inner], w [hidden, inner], residual [rows, hidden], gate_mod / mod [mod rows, slots, hidden]
+    bf16 bit patterns; row_map uint32 [rows]. Returns (gated, output or None)."""
+    residual, x, w, norm_weight, gate_mod, mod = _c(residual, x, w, norm_weight, gate_mod, mod)
+    row_map = np.ascontiguousarray(row_map, dtype=np.uint32)
+    rows, inner = x.shape
+    hidden = w.shape[0]
+    gated = np.empty((rows, hidden), dtype=np.uint16)
+    out = np.empty((rows, hidden), dtype=np.uint16) if adaln else None
+    lib().oracle_out_proj_gate_adaln(_p(gated), _p(out) if adaln else None, _p(residual), _p(x), _p(w),
+                                     _p(norm_weight), _p(gate_mod), _p(mod), _p(row_map), rows, inner, hidden,
+                                     slots, gate_slot, shift_slot, scale_slot, C.c_float(epsilon))
+    return gated, out
+
+
 def set_threads(threads):
     """Use `threads` OpenMP threads from now on; returns the count in effect."""
     lib().oracle_set_threads(int(threads))

@@ -91,3 +91,17 @@ def assert_rope_close(oracle, got, want):
     assert (d != 0).mean() < 2e-3, "too many elements differ"
     assert d[..., 2 * ROPE_HALF:].max() <= 1, "more than one bf16 step"
     assert np.abs(oracle.from_bf16(got) - oracle.from_bf16(want))[..., :2 * ROPE_HALF].max() <= 2.0 ** -4
+
+
+def out_proj_inputs(oracle, rows, inner, hidden, seed, slots=6, mod_rows=3):
+    """Seeded inputs of the attention output projection + gate + AdaLN chain (h3_dit.c:2573-2597):
+    attention heads, projection weight [hidden][inner], residual stream, norm weight, modulation
+    [mod_rows][slots][hidden], row map."""
+    rng = np.random.default_rng(seed)
+    x = oracle.normal_bf16((rows, inner), seed, 0.5)
+    w = oracle.to_bf16((rng.standard_normal((hidden, inner)) / np.sqrt(inner)).astype(np.float32))
+    residual = oracle.normal_bf16((rows, hidden), seed + 1)
+    norm_weight = oracle.to_bf16(1.0 + 0.1 * rng.standard_normal(hidden).astype(np.float32))
+    modulation = oracle.to_bf16(0.3 * rng.standard_normal((mod_rows, slots, hidden)).astype(np.float32))
+    row_map = rng.integers(0, mod_rows, rows).astype(np.uint32)
+    return x, w, residual, norm_weight, modulation, row_map

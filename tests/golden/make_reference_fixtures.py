@@ -9,6 +9,8 @@ see oracle/ref_build.py). Everything stored here is computed by REFERENCE code:
   reference_vsa_*.npz    : tile map, sizes, tiled Q, pooled means (tile_pool), pooled scores after
                            the in-place softmax (cuBLAS SGEMM + pooled_softmax), index lists and
                            counts (select_blocks), compression (cuBLAS SGEMM)
+  reference_out_proj.npz : attention output projection (h3_gpu_linear_bf16, cuBLAS), gate + AdaLN
+                           (h3_gpu_gate_adaln_bf16, cuda/fast_primitives.cuh:50-124)
 The merged VSA output is NOT stored: its fine stage runs this repository's kernel.
 Inputs are regenerated from seeds by the oracle's generator, so only outputs are stored.
 """
@@ -23,11 +25,12 @@ sys.path.insert(0, str(ROOT / "tests"))
 import __graft_entry__ as entry  # noqa: E402
 import ctypes as C  # noqa: E402
 
-from conftest import ROPE_HALF, rope_inputs  # noqa: E402
+from conftest import ROPE_HALF, out_proj_inputs, rope_inputs  # noqa: E402
 from refbackend import Reference, ref_vsa_buffers  # noqa: E402
 
 SDPA_CASE = dict(L=130, H=2, seed=31)
 ROPE_CASE = dict(rows=37, heads=5, seed=61)
+OUT_PROJ_CASE = dict(rows=37, inner=192, hidden=1024, seed=81, slots=6, gate=2, shift=3, scale=4)
 VSA_CASES = [dict(text=3, audio=11, shape=(1, 2, 3), heads=2, seed=700),
              dict(text=65, audio=67, shape=(5, 7, 9), heads=2, seed=710),
              dict(text=17, audio=30, shape=(7, 8, 8), heads=3, seed=720)]
@@ -58,6 +61,23 @@ def main(out_dir):
         for which, t in zip("qkv", outs):
             stored[name + "_" + which] = ref.read(t, (c["rows"], c["heads"], 128))
     np.savez_compressed(out_dir / "reference_qkv_rope.npz", **stored)
+    c = OUT_PROJ_CASE
+    x, w, residual, norm_weight, modulation, row_map = out_proj_inputs(oracle, c["rows"], c["inner"], c["hidden"], c["seed"])
+    L = ref.lib
+    L.h3_gpu_tensor_from_u32.restype = C.c_void_p
+    L.h3_gpu_tensor_from_u32.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    L.h3_gpu_linear_bf16.argtypes = [C.c_void_p] * 5 + [C.c_uint32] * 3
+    L.h3_gpu_gate_adaln_bf16.argtypes = [C.c_void_p] * 9 + [C.c_uint32] * 6 + [C.c_float]
+    tmap = L.h3_gpu_tensor_from_u32(ref.gpu, row_map.ctypes.data_as(C.c_void_p), row_map.size)
+    n = c["rows"] * c["hidden"]
+    y, gated, out = ref.empty(n), ref.empty(n), ref.empty(n)
+    tmod = ref.tensor(modulation)
+    ref.check(L.h3_gpu_linear_bf16(ref.gpu, y, ref.tensor(x), ref.tensor(w), None, c["rows"], c["inner"], c["hidden"]), "linear")
+    ref.check(L.h3_gpu_gate_adaln_bf16(ref.gpu, gated, out, ref.tensor(residual), y, ref.tensor(norm_weight), tmod, tmod, tmap,
+                                       c["rows"], c["hidden"], c["slots"], c["gate"], c["shift"], c["scale"], 1e-5), "gate_adaln")
+    shape = (c["rows"], c["hidden"])
+    np.savez_compressed(out_dir / "reference_out_proj.npz", y=ref.read(y, shape), gated=ref.read(gated, shape),
+                        out=ref.read(out, shape), **c)
     for n, c in enumerate(VSA_CASES):
         vmap = oracle.VsaMap(c["text"], c["audio"], *c["shape"])
         T, H = vmap.tiles, c["heads"]

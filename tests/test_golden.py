@@ -11,7 +11,7 @@ from pathlib import Path
 import numpy as np
 import pytest
 
-from conftest import ROPE_HALF, assert_rope_close, rope_inputs
+from conftest import ROPE_HALF, assert_rope_close, bf16_step_distance, out_proj_inputs, rope_inputs
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
@@ -67,3 +67,22 @@ def test_vsa_coarse_stage_matches_reference(oracle, n):
     # pooled softmax and compression: FP32 rounding of a different summation order
     assert np.abs(s["prob"] - g["prob"]).max() < 1e-6
     assert np.abs(s["compression"] - g["compression"]).max() < 2e-5
+
+
+def test_out_projection_gate_adaln_matches_reference(oracle):
+    """h3_gpu_linear_bf16 (cuBLAS) + h3_gpu_gate_adaln_bf16 of the reference against the oracle's
+    restatement: the projection sums in another order (a bf16 rounding flips now and then), gate
+    and AdaLN follow the reference kernel's operation order."""
+    g = np.load(GOLDEN / "reference_out_proj.npz")
+    c = {k: int(g[k]) for k in ("rows", "inner", "hidden", "seed", "slots", "gate", "shift", "scale")}
+    x, w, residual, norm_weight, modulation, row_map = out_proj_inputs(oracle, c["rows"], c["inner"], c["hidden"], c["seed"])
+    gated, out = oracle.out_proj_gate_adaln(residual, x, w, norm_weight, modulation, modulation, row_map, c["slots"],
+                                            c["gate"], c["shift"], c["scale"])
+    for mine, name in ((gated, "gated"), (out, "out")):
+        d = bf16_step_distance(mine, g[name])
+        assert (d != 0).mean() < 0.01, name
+        assert np.abs(oracle.from_bf16(mine) - oracle.from_bf16(g[name])).max() <= 2.0 ** -5, name
+    # AdaLN on the reference's own gated rows: only 1/sqrtf against the GPU's approximate rsqrtf remains
+    _, exact = oracle.out_proj_gate_adaln(g["gated"], x, np.zeros_like(w), norm_weight, np.zeros_like(modulation),
+                                          modulation, row_map, c["slots"], c["gate"], c["shift"], c["scale"])
+    assert (exact != g["out"]).mean() < 0.005
