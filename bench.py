@@ -656,6 +656,17 @@ def dit_step(env, plan, heads, blocks=50, steps=2):
     F = torch.nn.functional
     exchange, slots = env.make_exchange(rows * heads * DIM, 4) if world > 1 else (None, None)
     scale = float(1.0 / np.sqrt(128.0))
+    # what follows attention (output projection, gate, residual, AdaLN of the MLP input) is this
+    # library's fused call; at N > 1 it reads the rows the attention kernel gathered straight from
+    # the window slot
+    w_out_t = w_out.t().contiguous()                         # [hidden][inner], the reference's weight layout
+    ones = torch.ones(hidden, device=device, dtype=torch.bfloat16)
+    mod6 = mod.view(1, 6, hidden).contiguous()
+    row_map = torch.zeros(rows, dtype=torch.int32, device=device)
+    t_w, t_ones, t_mod = env.wrap(w_out_t), env.wrap(ones), env.wrap(mod6)
+    t_map = gpu.wrap(row_map.data_ptr(), rows, 3)
+    normed = torch.empty(rows, hidden, device=device, dtype=torch.bfloat16)
+    t_normed = env.wrap(normed)
 
     def norm_mod(x, scale_, shift):
         return F.rms_norm(x, (hidden,)) * (1 + scale_) + shift
@@ -674,13 +685,19 @@ def dit_step(env, plan, heads, blocks=50, steps=2):
                 if not lib.h3b_exchange_sdpa_gather_bf16(exchange, 3, slots[0], slots[1], slots[2], plan.sequence,
                                                          rows, heads, scale):
                     raise RuntimeError(gpu.error())
-                gpu.call("copy_bf16", to, 0, slots[3], 0, rows * heads * DIM)   # window -> torch tensor
+                attended = slots[3]
             else:
                 gpu.call("qkv_rope_bf16", tq, tk, tv, tqkv, *rope, rows, heads, DIM, 48, 1e-5)
                 gpu.call("sdpa_bf16", to, tq, tk, tv, plan.sequence, local_heads, DIM, scale)
+                attended = to
             gpu.free(tqkv)
-            x = x + mod[2] * (o.view(rows, inner) @ w_out)
-            h = norm_mod(x, mod[3], mod[4])
+            tx = env.wrap(x)
+            # in place over the residual stream, as the reference does (hidden is both input and output)
+            if not lib.h3b_attention_output_gate_adaln_bf16(gpu.gpu, tx, t_normed, tx, attended, t_w, t_ones, t_mod,
+                                                            t_mod, t_map, rows, inner, hidden, 6, 2, 3, 4, C.c_float(1e-5)):
+                raise RuntimeError(gpu.error())
+            gpu.free(tx)
+            h = normed
             u = h @ w_fc1
             x = x + mod[5] * ((F.silu(u[:, :ffn]) * u[:, ffn:]) @ w_fc2)
         if world > 1:
@@ -694,7 +711,8 @@ def dit_step(env, plan, heads, blocks=50, steps=2):
     gemm_flops = 2.0 * plan.sequence * (hidden * 3 * inner + inner * hidden + hidden * 2 * ffn + ffn * hidden) * blocks
     attn_flops = 4.0 * plan.sequence ** 2 * heads * DIM * blocks
     return {"workload": "50-block DiT denoising step, L=%d, H=%d, hidden %d, FFN %d; norm/RoPE, attention, Ulysses "
-                        "exchanges from this library; GEMMs and other elementwise ops torch" % (plan.sequence, heads, hidden, ffn),
+                        "exchanges, output projection + gate + AdaLN from this library; the other GEMMs and elementwise ops "
+                        "torch" % (plan.sequence, heads, hidden, ffn),
             "ms_per_step": ms, "n_gpus": world, "steps": steps, "blocks": blocks,
             "model_tflops": (gemm_flops + attn_flops) / ms / 1e9}
 

@@ -653,7 +653,8 @@ attn_sparse_t_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 // memory per multiply-add; this kernel multiplies each tile by its own list only. Measured cost:
 // about 990 cycles per union tile there, 692 cycles per list entry here, so a pair goes to the
 // pair walk when |A u B| < 0.7 (|A| + |B|) - lists that mostly coincide, as neighbouring cubes of
-// real video tend to produce - and stays here otherwise. One warp per pair; both lists ascending.
+// real video tend to produce - and stays here otherwise (also when the union is longer than 256
+// tiles). One warp per pair; both lists ascending.
 __global__ void __launch_bounds__(256)
 pair_choice_kernel(const int *__restrict__ indices, const int *__restrict__ counts, unsigned char *elsewhere,
                    unsigned char *redo, int tiles, int heads, int force) {
@@ -682,7 +683,12 @@ pair_choice_kernel(const int *__restrict__ indices, const int *__restrict__ coun
             if (kt >= 0 && kt < tiles) common += (bits[warp][kt >> 5] >> (kt & 31)) & 1u;
         }
         common = __reduce_add_sync(0xffffffffu, common);
-        choice = 10 * (na + nb - common) < 7 * (na + nb) ? 1 : 0;
+        // Long lists stay with the persistent kernel whatever their overlap: there they are one
+        // ticket among thousands, while a pair-walk CTA walks its whole union alone (the prefix
+        // tiles of a video - every query tile attends all 905 KV tiles - would leave 96 CTAs
+        // running for a millisecond after everything else has finished).
+        const int joined = na + nb - common;
+        choice = (10 * joined < 7 * (na + nb) && joined <= 256) ? 1 : 0;
     }
     if (lane == 0) {
         elsewhere[row] = redo[row] = (unsigned char)choice;
