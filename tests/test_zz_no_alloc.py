@@ -47,6 +47,40 @@ def static_path(gpu, case):
             gpu.read(counts, (heads, tiles), np.int32))
 
 
+def free_device_bytes():
+    """Free device memory as the CUDA runtime reports it (after everything queued has run)."""
+    from h3_omni_b200 import native
+    rt = native._cudart()
+    free, total = C.c_size_t(), C.c_size_t()
+    assert rt.cudaDeviceSynchronize() == 0
+    assert rt.cudaMemGetInfo(C.byref(free), C.byref(total)) == 0
+    return free.value
+
+
+def test_static_topk_leaves_device_memory_as_it_found_it(gpu, oracle):
+    """The point of the entry point: a call allocates nothing. The tensors of the call are made
+    first, one call runs to set the scratch address up, then the amount of free device memory is
+    read before and after two more calls (on the stream, no tensor created in between)."""
+    case = regular_path(gpu, oracle, 17, 30, (7, 8, 8), 3, 4400)
+    try:
+        heads, tiles = case["heads"], case["tiles"]
+        indices = gpu.tensor(np.zeros((heads, tiles, tiles), dtype=np.int32))
+        counts = gpu.tensor(np.zeros((heads, tiles), dtype=np.int32))
+        data, stream = gpu.lib.h3b_tensor_data, gpu.lib.h3b_gpu_stream(gpu.gpu)
+
+        def call():
+            return gpu.lib.h3b_vsa_topk_static(data(case["q"]), data(case["k"]), case["map"], case["sizes"], data(indices),
+                                               data(counts), tiles, case["prefix"], case["keep"], heads, stream)
+
+        assert call() == 0
+        before = free_device_bytes()
+        assert call() == 0 and call() == 0
+        assert free_device_bytes() == before
+        same_lists(case, gpu.read(indices, (heads, tiles, tiles), np.int32), gpu.read(counts, (heads, tiles), np.int32))
+    finally:
+        gpu.lib.h3_gpu_vsa_free(case["handle"])
+
+
 def same_lists(case, indices, counts):
     assert np.array_equal(counts, case["counts"])
     valid = np.arange(case["tiles"])[None, None, :] < counts[:, :, None]
