@@ -13,6 +13,14 @@
 //   warp 8          : TMA producer
 //   warp 9          : MMA issuer      (warps 8-11 give most of their registers to the
 //                                      softmax warpgroups with setmaxnreg)
+//   warp 10         : watches the K/V ring for the issuer (see below)
+// Whatever the issuing thread does between two batches of MMAs leaves the tensor pipe idle (its
+// queue is short), and a probe of an mbarrier costs that thread 80-100 cycles even when the
+// barrier is long complete. So the issuer waits on exactly two barriers per step, P_A and P_B:
+// K/V arrive in pairs (V_j, K_j+1) under one barrier, a thread of warp 10 waits for the pair and
+// adds its arrival to P_A's barrier; one commit per step frees the pair; and the softmax threads
+// need no "PV done" signal inside the loop because the commit that announces S(j) also covers
+// PV(j-1), issued before it by the same thread.
 // A fixed fraction of the exponentials is evaluated by a polynomial on the FMA pipe (see
 // softmax_tc5.cuh) so the exponential unit is not the critical resource.
 // Serves h3_flash3_bf16 / h3_flash3_cross_bf16 / non-causal h3_flash_bf16 whenever the call
@@ -27,7 +35,7 @@ namespace {
 
 constexpr int PBM = 128, PBN = 128, PHD = 128;
 constexpr int PAIR_THREADS = 384;                  // three warpgroups: softmax A, softmax B, {TMA, MMA}
-constexpr int PAIR_STAGES = 4;                      // K0 V0 K1 V1 ... ring of 32 KB tiles
+constexpr int PAIR_STAGES = 4;                      // K0 V0 K1 V1 ... ring of 32 KB tiles, handed over as pairs (V_j, K_j+1)
 constexpr int PAIR_TILE_BYTES = PBN * PHD * 2;      // 32 KB
 constexpr int PAIR_HALF_BYTES = PBN * 128;          // one 64-column half
 constexpr int PAIR_Q_BYTES = 2 * PBM * PHD * 2;     // 64 KB
@@ -75,7 +83,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                      const PairParams p) {
     constexpr int ST = PAIR_STAGES;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[1 + 2 * ST + 6];
+    __shared__ uint64_t bars[1 + 4 + 5];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_word;
 
@@ -86,11 +94,12 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t bar_q_full = bar0;
-    auto bar_full = [&](int s) { return bar0 + 8u * (1 + s); };
-    auto bar_empty = [&](int s) { return bar0 + 8u * (1 + ST + s); };
-    auto bar_s_full = [&](int t) { return bar0 + 8u * (1 + 2 * ST + t); };
-    auto bar_p_full = [&](int t) { return bar0 + 8u * (1 + 2 * ST + 2 + t); };
-    auto bar_pv_done = [&](int t) { return bar0 + 8u * (1 + 2 * ST + 4 + t); };
+    // pair g = (V_g, K_g+1) lives in ring slots (2g+1) % ST and (2g+2) % ST; its barriers are g % 2
+    auto bar_full = [&](int g) { return bar0 + 8u * (1 + (g & 1)); };
+    auto bar_empty = [&](int g) { return bar0 + 8u * (3 + (g & 1)); };
+    auto bar_s_full = [&](int t) { return bar0 + 8u * (5 + t); };
+    auto bar_p_full = [&](int t) { return bar0 + 8u * (7 + t); };
+    const uint32_t bar_pv_done = bar0 + 8u * 9;   // the last PV of both tiles
 
     const int head = blockIdx.y, batch = p.split_tiles ? 0 : blockIdx.z, out_batch = blockIdx.z;
     const int kv_head = head / (p.heads / p.kv_heads);
@@ -104,15 +113,14 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
     if (tid == 0) {
         mbar_init(bar_q_full, 1);
-        for (int s = 0; s < ST; s++) {
-            mbar_init(bar_full(s), 1);
-            mbar_init(bar_empty(s), 1);
+        for (int g = 0; g < 2; g++) {
+            mbar_init(bar_full(g), 1);
+            mbar_init(bar_empty(g), 1);
         }
-        for (int t = 0; t < 2; t++) {
-            mbar_init(bar_s_full(t), 1);
-            mbar_init(bar_p_full(t), 128);
-            mbar_init(bar_pv_done(t), 1);
-        }
+        for (int t = 0; t < 2; t++) mbar_init(bar_s_full(t), 1);
+        mbar_init(bar_p_full(0), 128 + 1);   // the softmax threads of tile A and the ring watcher
+        mbar_init(bar_p_full(1), 128);
+        mbar_init(bar_pv_done, 1);
         mbar_fence_init();
         abort_word = 0;
     }
@@ -131,30 +139,38 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             tma_prefetch_desc(&map_q);
-            mbar_arrive_expect_tx(bar_q_full, PAIR_Q_BYTES);
+            // Q and the first K tile share a barrier; after that one barrier per pair (V_j, K_j+1)
+            mbar_arrive_expect_tx(bar_q_full, PAIR_Q_BYTES + PAIR_TILE_BYTES);
             for (int t = 0; t < 2; t++) {
                 const uint32_t dst = q_smem + t * (PAIR_Q_BYTES / 2);
                 tma_load_4d(dst, &map_q, bar_q_full, 0, head, q_row0 + t * PBM, batch);
                 tma_load_4d(dst + PAIR_HALF_BYTES, &map_q, bar_q_full, 64, head, q_row0 + t * PBM, batch);
             }
-            int idx = 0;   // ring position: even = K tile, odd = V tile
-            bool ok = true;
-            for (int seg = 0; ok && seg < p.segments; seg++) {
-                const int tiles = (seg_rows(seg) + PBN - 1) / PBN;
-                for (int tile = 0; ok && tile < tiles; tile++) {
-                    for (int which = 0; which < 2; which++, idx++) {
-                        const int s = idx % ST, use = idx / ST;
-                        if (use > 0 && !mbar_wait(bar_empty(s), (use - 1) & 1, &abort_word)) {
-                            ok = false;
-                            break;
-                        }
-                        const uint32_t dst = ring + s * PAIR_TILE_BYTES;
-                        const void *map = which ? (const void *)&kv.v[seg] : (const void *)&kv.k[seg];
-                        mbar_arrive_expect_tx(bar_full(s), PAIR_TILE_BYTES);
-                        tma_load_4d(dst, map, bar_full(s), 0, kv_head, (tile0 + tile) * PBN, batch);
-                        tma_load_4d(dst + PAIR_HALF_BYTES, map, bar_full(s), 64, kv_head, (tile0 + tile) * PBN, batch);
-                    }
+            auto load_tile = [&](const void *map, int slot, int tile, uint32_t bar) {
+                const uint32_t dst = ring + slot * PAIR_TILE_BYTES;
+                tma_load_4d(dst, map, bar, 0, kv_head, (tile0 + tile) * PBN, batch);
+                tma_load_4d(dst + PAIR_HALF_BYTES, map, bar, 64, kv_head, (tile0 + tile) * PBN, batch);
+            };
+            load_tile(&kv.k[0], 0, 0, bar_q_full);
+            // two cursors over the ranges: V of step g, K of step g + 1
+            int v_seg = 0, v_tile = 0, k_seg = 0, k_tile = 0;
+            auto advance = [&](int &seg, int &tile) {
+                if (++tile * PBN >= seg_rows(seg)) {
+                    seg++;
+                    tile = 0;
                 }
+            };
+            advance(k_seg, k_tile);
+            for (int g = 0; g < n_tiles; g++) {
+                if (g >= 2 && !mbar_wait(bar_empty(g), ((g >> 1) - 1) & 1, &abort_word)) break;
+                const bool more = g + 1 < n_tiles;
+                mbar_arrive_expect_tx(bar_full(g), more ? 2 * PAIR_TILE_BYTES : PAIR_TILE_BYTES);
+                load_tile(&kv.v[v_seg], (2 * g + 1) % ST, v_tile, bar_full(g));
+                // K_2 goes where K_0 is: not before both first QK products have been computed
+                if (g == 1 && !mbar_wait(bar_s_full(1), 0, &abort_word)) break;
+                if (more) load_tile(&kv.k[k_seg], (2 * g + 2) % ST, k_tile, bar_full(g));
+                advance(v_seg, v_tile);
+                if (more) advance(k_seg, k_tile);
             }
         }
     } else if (warp == 9) {
@@ -162,9 +178,6 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         if (lane == 0) {
             constexpr uint32_t idesc_qk = mma_idesc(PBM, PBN, 1, 0);
             constexpr uint32_t idesc_pv = mma_idesc(PBM, PHD, 1, 1);
-            auto wait_stage = [&](int idx) {
-                return mbar_wait(bar_full(idx % ST), (idx / ST) & 1, &abort_word);
-            };
             // Descriptors are built once (Q) or once per stage (K, V); a K-step only adds to
             // the low word: +2 per 32 bytes inside a 64-column half, +1024 for the second half
             // (16 KB), +128 per 16 V rows (2 KB).
@@ -186,7 +199,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     mma_ss_words(tmem + t * PBN, q_lo[t] + off, q_hi[t], k_lo + off, k_hi, idesc_qk,
                                  kk > 0);
                 }
-                mma_commit(bar_s_full(t));
+                mma_commit(bar_s_full(t));   // also tells the softmax threads that PV_t(j-1) is complete
             };
             auto issue_pv = [&](int j, int t) {   // O_t += P_t . V_j
                 const uint32_t v_lo = v_ring_lo + ((2 * j + 1) % ST) * (PAIR_TILE_BYTES >> 4);
@@ -194,34 +207,21 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 for (int kk = 0; kk < PBN / 16; kk++)
                     mma_ts_words(tmem + PAIR_O_COL + t * PHD, tmem + t * PBN + kk * 8,
                                  v_lo + kk * (2048 >> 4), v_hi, idesc_pv, (j > 0) || (kk > 0));
-                mma_commit(bar_pv_done(t));
             };
 #ifdef H3B_TRACE
             long long g_pair_trace_local[8] = {};
             const long long trace_begin = clock64();
 #endif
-            bool alive = mbar_wait(bar_q_full, 0, &abort_word) && wait_stage(0);
+            bool alive = mbar_wait(bar_q_full, 0, &abort_word);
             if (alive) {
                 tc5_fence_after();
                 issue_qk(0, 0);
                 issue_qk(0, 1);
-                mma_commit(bar_empty(0));
             }
             for (int j = 0; alive && j < n_tiles; j++) {
                 const bool more = j + 1 < n_tiles;
-                // K/V of this step were requested a step ago; probe them first so that these
-                // (normally immediate) waits are off the path between P arriving and the PV issue.
                 {
-                    TRACE_T0();
-                    if (!wait_stage(2 * j + 1)) break;
-                    TRACE_ADD(1);
-                }
-                if (more) {
-                    TRACE_T0();
-                    if (!wait_stage(2 * j + 2)) break;
-                    TRACE_ADD(2);
-                }
-                {
+                    // P of tile A, and (through the ring watcher) V of this step and K of the next
                     TRACE_T0();
                     if (!mbar_wait(bar_p_full(0), j & 1, &abort_word)) break;
                     TRACE_ADD(0);
@@ -244,24 +244,36 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
                 tc5_fence_after();
                 issue_pv(j, 1);
-                mma_commit(bar_empty((2 * j + 1) % ST));
                 if (more) {
                     issue_qk(j + 1, 1);
-                    mma_commit(bar_empty((2 * j + 2) % ST));
+                    mma_commit(bar_empty(j));     // V_j and K_j+1 have been read
+                } else {
+                    mma_commit(bar_pv_done);      // both accumulators are final
                 }
             }
 #ifdef H3B_TRACE
             if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
                 g_pair_trace[0] = clock64() - trace_begin;   // MMA thread: whole walk
                 g_pair_trace[1] = g_pair_trace_local[0];     // waiting for P of tile A
-                g_pair_trace[2] = g_pair_trace_local[1];     // waiting for V
-                g_pair_trace[3] = g_pair_trace_local[2];     // waiting for K
+                g_pair_trace[2] = 0;
+                g_pair_trace[3] = 0;
                 g_pair_trace[4] = g_pair_trace_local[3];     // waiting for P of tile B
                 g_pair_trace[5] = n_tiles;
                 g_pair_trace[6] = g_pair_trace_local[4];     // thread time inside issue_pv(A)
                 g_pair_trace[7] = g_pair_trace_local[5];     // thread time inside issue_qk(A)
             }
 #endif
+        }
+    } else if (warp == 10) {
+        // ------------------------------- ring watcher -------------------------------
+        if (lane == 0) {
+            // One arrival per phase of P_A's barrier: the next pair is often complete before the
+            // softmax threads are, so wait for the phase to end before arriving again.
+            for (int g = 0; g < n_tiles; g++) {
+                if (!mbar_wait(bar_full(g), (g >> 1) & 1, &abort_word)) break;
+                mbar_arrive(bar_p_full(0));
+                if (!mbar_wait(bar_p_full(0), g & 1, &abort_word)) break;
+            }
         }
     }
     } else {
@@ -296,7 +308,6 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #ifdef H3B_TRACE
             const long long trace_work = clock64();
 #endif
-            bool saw_prev_pv = (j == 0);
             if (nvalid >= PBN) {
                 // the whole row of scores in registers: one TMEM read pass
                 uint32_t s0[32], s1[32], s2[32], s3[32];
@@ -316,12 +327,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     const float alpha = grow ? fast_exp2((m_ref - m_new) * p.scale_log2) : 1.0f;
                     if (grow) m_ref = m_new;
                     l *= alpha;
-                    if (j > 0) {
-                        alive = __all_sync(0xffffffffu,
-                                           mbar_wait(bar_pv_done(t), (j - 1) & 1, &abort_word));
-                        if (!alive) break;
-                        saw_prev_pv = true;
-                        tc5_fence_after();
+                    if (j > 0) {   // PV(j-1) is complete: S(j)'s commit covered it
 #pragma unroll
                         for (int c = 0; c < PHD / 32; c++) {
                             uint32_t v[32];
@@ -358,12 +364,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     const float alpha = grow ? fast_exp2((m_ref - m_new) * p.scale_log2) : 1.0f;
                     if (grow) m_ref = m_new;
                     l *= alpha;
-                    if (j > 0) {
-                        alive = __all_sync(0xffffffffu,
-                                           mbar_wait(bar_pv_done(t), (j - 1) & 1, &abort_word));
-                        if (!alive) break;
-                        saw_prev_pv = true;
-                        tc5_fence_after();
+                    if (j > 0) {   // PV(j-1) is complete: S(j)'s commit covered it
 #pragma unroll
                         for (int c = 0; c < PHD / 32; c++) {
                             uint32_t v[32];
@@ -378,10 +379,6 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     }
                 }
                 l += exp_store_masked<PBN>(s_addr, s_addr, p.scale_log2, -m_ref * p.scale_log2, nvalid);
-            }
-            if (!saw_prev_pv) {
-                alive = __all_sync(0xffffffffu, mbar_wait(bar_pv_done(t), (j - 1) & 1, &abort_word));
-                if (!alive) break;
             }
             tmem_wait_st();
             tc5_fence_before();
@@ -399,7 +396,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #endif
 
         // -------- epilogue: O / l -> bf16, straight to global memory --------
-        if (alive) alive = __all_sync(0xffffffffu, mbar_wait(bar_pv_done(t), (n_tiles - 1) & 1, &abort_word));
+        if (alive) alive = __all_sync(0xffffffffu, mbar_wait(bar_pv_done, 0, &abort_word));
         if (alive) {
             tc5_fence_after();
             const float inv = 1.0f / l;
