@@ -17,10 +17,11 @@
 // Whatever the issuing thread does between two batches of MMAs leaves the tensor pipe idle (its
 // queue is short), and a probe of an mbarrier costs that thread 80-100 cycles even when the
 // barrier is long complete. So the issuer waits on exactly two barriers per step, P_A and P_B:
-// K/V arrive in pairs (V_j, K_j+1) under one barrier, a thread of warp 10 waits for the pair and
-// adds its arrival to P_A's barrier; one commit per step frees the pair; and the softmax threads
-// need no "PV done" signal inside the loop because the commit that announces S(j) also covers
-// PV(j-1), issued before it by the same thread.
+// a thread of warp 10 waits for V_j and K_j+1 to land and adds its arrival to P_A's barrier; and
+// the softmax threads need no "PV done" signal inside the loop because the commit that announces
+// S(j) also covers PV(j-1), issued before it by the same thread. The ring has five slots: a tile
+// takes 2000-3000 cycles from the request to shared memory when every SM asks at once, and with
+// four slots (two steps of K/V) the request for step j+2 cannot leave before step j is over.
 // A fixed fraction of the exponentials is evaluated by a polynomial on the FMA pipe (see
 // softmax_tc5.cuh) so the exponential unit is not the critical resource.
 // Serves h3_flash3_bf16 / h3_flash3_cross_bf16 / non-causal h3_flash_bf16 whenever the call
@@ -35,7 +36,7 @@ namespace {
 
 constexpr int PBM = 128, PBN = 128, PHD = 128;
 constexpr int PAIR_THREADS = 384;                  // three warpgroups: softmax A, softmax B, {TMA, MMA}
-constexpr int PAIR_STAGES = 4;                      // K0 V0 K1 V1 ... ring of 32 KB tiles, handed over as pairs (V_j, K_j+1)
+constexpr int PAIR_STAGES = 5;                      // K0 V0 K1 V1 ... ring of 32 KB tiles
 constexpr int PAIR_TILE_BYTES = PBN * PHD * 2;      // 32 KB
 constexpr int PAIR_HALF_BYTES = PBN * 128;          // one 64-column half
 constexpr int PAIR_Q_BYTES = 2 * PBM * PHD * 2;     // 64 KB
@@ -83,7 +84,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                      const PairParams p) {
     constexpr int ST = PAIR_STAGES;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[1 + 4 + 5];
+    __shared__ uint64_t bars[1 + 2 * ST + 5];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_word;
 
@@ -94,12 +95,12 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t bar_q_full = bar0;
-    // pair g = (V_g, K_g+1) lives in ring slots (2g+1) % ST and (2g+2) % ST; its barriers are g % 2
-    auto bar_full = [&](int g) { return bar0 + 8u * (1 + (g & 1)); };
-    auto bar_empty = [&](int g) { return bar0 + 8u * (3 + (g & 1)); };
-    auto bar_s_full = [&](int t) { return bar0 + 8u * (5 + t); };
-    auto bar_p_full = [&](int t) { return bar0 + 8u * (7 + t); };
-    const uint32_t bar_pv_done = bar0 + 8u * 9;   // the last PV of both tiles
+    // tile number 2j is K_j, 2j+1 is V_j; tile i lives in slot i % ST and is that slot's use i / ST
+    auto bar_full = [&](int s) { return bar0 + 8u * (1 + s); };
+    auto bar_empty = [&](int s) { return bar0 + 8u * (1 + ST + s); };
+    auto bar_s_full = [&](int t) { return bar0 + 8u * (1 + 2 * ST + t); };
+    auto bar_p_full = [&](int t) { return bar0 + 8u * (1 + 2 * ST + 2 + t); };
+    const uint32_t bar_pv_done = bar0 + 8u * (1 + 2 * ST + 4);   // the last PV of both tiles
 
     const int head = blockIdx.y, batch = p.split_tiles ? 0 : blockIdx.z, out_batch = blockIdx.z;
     const int kv_head = head / (p.heads / p.kv_heads);
@@ -113,9 +114,9 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
     if (tid == 0) {
         mbar_init(bar_q_full, 1);
-        for (int g = 0; g < 2; g++) {
-            mbar_init(bar_full(g), 1);
-            mbar_init(bar_empty(g), 1);
+        for (int s = 0; s < ST; s++) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_empty(s), 1);
         }
         for (int t = 0; t < 2; t++) mbar_init(bar_s_full(t), 1);
         mbar_init(bar_p_full(0), 128 + 1);   // the softmax threads of tile A and the ring watcher
@@ -139,43 +140,39 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             tma_prefetch_desc(&map_q);
-            // Q and the first K tile share a barrier; after that one barrier per pair (V_j, K_j+1)
-            mbar_arrive_expect_tx(bar_q_full, PAIR_Q_BYTES + PAIR_TILE_BYTES);
+            mbar_arrive_expect_tx(bar_q_full, PAIR_Q_BYTES);
             for (int t = 0; t < 2; t++) {
                 const uint32_t dst = q_smem + t * (PAIR_Q_BYTES / 2);
                 tma_load_4d(dst, &map_q, bar_q_full, 0, head, q_row0 + t * PBM, batch);
                 tma_load_4d(dst + PAIR_HALF_BYTES, &map_q, bar_q_full, 64, head, q_row0 + t * PBM, batch);
             }
-            auto load_tile = [&](const void *map, int slot, int tile, uint32_t bar) {
-                const uint32_t dst = ring + slot * PAIR_TILE_BYTES;
-                tma_load_4d(dst, map, bar, 0, kv_head, (tile0 + tile) * PBN, batch);
-                tma_load_4d(dst + PAIR_HALF_BYTES, map, bar, 64, kv_head, (tile0 + tile) * PBN, batch);
-            };
-            load_tile(&kv.k[0], 0, 0, bar_q_full);
-            // two cursors over the ranges: V of step g, K of step g + 1
-            int v_seg = 0, v_tile = 0, k_seg = 0, k_tile = 0;
-            auto advance = [&](int &seg, int &tile) {
-                if (++tile * PBN >= seg_rows(seg)) {
-                    seg++;
-                    tile = 0;
+            int idx = 0;   // tile number: even = K, odd = V
+            bool ok = true;
+            for (int seg = 0; ok && seg < p.segments; seg++) {
+                const int tiles = (seg_rows(seg) + PBN - 1) / PBN;
+                for (int tile = 0; ok && tile < tiles; tile++) {
+                    for (int which = 0; which < 2; which++, idx++) {
+                        const int s = idx % ST, use = idx / ST;
+                        if (use > 0 && !mbar_wait(bar_empty(s), (use - 1) & 1, &abort_word)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t dst = ring + s * PAIR_TILE_BYTES;
+                        const void *map = which ? (const void *)&kv.v[seg] : (const void *)&kv.k[seg];
+                        mbar_arrive_expect_tx(bar_full(s), PAIR_TILE_BYTES);
+                        tma_load_4d(dst, map, bar_full(s), 0, kv_head, (tile0 + tile) * PBN, batch);
+                        tma_load_4d(dst + PAIR_HALF_BYTES, map, bar_full(s), 64, kv_head, (tile0 + tile) * PBN, batch);
+                    }
                 }
-            };
-            advance(k_seg, k_tile);
-            for (int g = 0; g < n_tiles; g++) {
-                if (g >= 2 && !mbar_wait(bar_empty(g), ((g >> 1) - 1) & 1, &abort_word)) break;
-                const bool more = g + 1 < n_tiles;
-                mbar_arrive_expect_tx(bar_full(g), more ? 2 * PAIR_TILE_BYTES : PAIR_TILE_BYTES);
-                load_tile(&kv.v[v_seg], (2 * g + 1) % ST, v_tile, bar_full(g));
-                // K_2 goes where K_0 is: not before both first QK products have been computed
-                if (g == 1 && !mbar_wait(bar_s_full(1), 0, &abort_word)) break;
-                if (more) load_tile(&kv.k[k_seg], (2 * g + 2) % ST, k_tile, bar_full(g));
-                advance(v_seg, v_tile);
-                if (more) advance(k_seg, k_tile);
             }
         }
     } else if (warp == 9) {
         // ------------------------------- MMA issuer -------------------------------
-        if (lane == 0) {
+        // The whole warp walks the loop and one elected lane issues: with the loop inside a
+        // one-lane branch every descriptor word is per-thread data that has to be moved to a
+        // uniform register in front of each MMA.
+        {
+            const bool leader = elect_one();
             constexpr uint32_t idesc_qk = mma_idesc(PBM, PBN, 1, 0);
             constexpr uint32_t idesc_pv = mma_idesc(PBM, PHD, 1, 1);
             // Descriptors are built once (Q) or once per stage (K, V); a K-step only adds to
@@ -193,37 +190,48 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const uint32_t k_ring_lo = (uint32_t)k_proto, v_ring_lo = (uint32_t)v_proto;  // LBO lives in the low word
             auto issue_qk = [&](int j, int t) {   // S_t = Q_t . K_j^T
                 const uint32_t k_lo = k_ring_lo + ((2 * j) % ST) * (PAIR_TILE_BYTES >> 4);
+                if (leader) {
 #pragma unroll
-                for (int kk = 0; kk < PHD / 16; kk++) {
-                    const uint32_t off = (kk / 4) * (PAIR_HALF_BYTES >> 4) + (kk % 4) * 2;
-                    mma_ss_words(tmem + t * PBN, q_lo[t] + off, q_hi[t], k_lo + off, k_hi, idesc_qk,
-                                 kk > 0);
+                    for (int kk = 0; kk < PHD / 16; kk++) {
+                        const uint32_t off = (kk / 4) * (PAIR_HALF_BYTES >> 4) + (kk % 4) * 2;
+                        mma_ss_words(tmem + t * PBN, q_lo[t] + off, q_hi[t], k_lo + off, k_hi, idesc_qk,
+                                     kk > 0);
+                    }
+                    mma_commit(bar_s_full(t));   // also tells the softmax threads that PV_t(j-1) is complete
                 }
-                mma_commit(bar_s_full(t));   // also tells the softmax threads that PV_t(j-1) is complete
+                __syncwarp();
             };
             auto issue_pv = [&](int j, int t) {   // O_t += P_t . V_j
                 const uint32_t v_lo = v_ring_lo + ((2 * j + 1) % ST) * (PAIR_TILE_BYTES >> 4);
+                if (leader) {
 #pragma unroll
-                for (int kk = 0; kk < PBN / 16; kk++)
-                    mma_ts_words(tmem + PAIR_O_COL + t * PHD, tmem + t * PBN + kk * 8,
-                                 v_lo + kk * (2048 >> 4), v_hi, idesc_pv, (j > 0) || (kk > 0));
+                    for (int kk = 0; kk < PBN / 16; kk++)
+                        mma_ts_words(tmem + PAIR_O_COL + t * PHD, tmem + t * PBN + kk * 8,
+                                     v_lo + kk * (2048 >> 4), v_hi, idesc_pv, (j > 0) || (kk > 0));
+                }
+                __syncwarp();
             };
 #ifdef H3B_TRACE
             long long g_pair_trace_local[8] = {};
             const long long trace_begin = clock64();
 #endif
-            bool alive = mbar_wait(bar_q_full, 0, &abort_word);
+            auto release = [&](int tile) {   // the slot may be refilled once the MMAs issued so far are done
+                if (leader) mma_commit(bar_empty(tile % ST));
+            };
+            bool alive = mbar_wait_converged(bar_q_full, 0, &abort_word) &&
+                         mbar_wait_converged(bar_full(0), 0, &abort_word);
             if (alive) {
                 tc5_fence_after();
                 issue_qk(0, 0);
                 issue_qk(0, 1);
+                release(0);
             }
             for (int j = 0; alive && j < n_tiles; j++) {
                 const bool more = j + 1 < n_tiles;
                 {
                     // P of tile A, and (through the ring watcher) V of this step and K of the next
                     TRACE_T0();
-                    if (!mbar_wait(bar_p_full(0), j & 1, &abort_word)) break;
+                    if (!mbar_wait_converged(bar_p_full(0), j & 1, &abort_word)) break;
                     TRACE_ADD(0);
                 }
                 tc5_fence_after();
@@ -239,20 +247,22 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
                 {
                     TRACE_T0();
-                    if (!mbar_wait(bar_p_full(1), j & 1, &abort_word)) break;
+                    if (!mbar_wait_converged(bar_p_full(1), j & 1, &abort_word)) break;
                     TRACE_ADD(3);
                 }
                 tc5_fence_after();
                 issue_pv(j, 1);
+                release(2 * j + 1);
                 if (more) {
                     issue_qk(j + 1, 1);
-                    mma_commit(bar_empty(j));     // V_j and K_j+1 have been read
-                } else {
+                    release(2 * j + 2);
+                } else if (leader) {
                     mma_commit(bar_pv_done);      // both accumulators are final
                 }
+                __syncwarp();
             }
 #ifdef H3B_TRACE
-            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0) {
                 g_pair_trace[0] = clock64() - trace_begin;   // MMA thread: whole walk
                 g_pair_trace[1] = g_pair_trace_local[0];     // waiting for P of tile A
                 g_pair_trace[2] = 0;
@@ -267,10 +277,12 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     } else if (warp == 10) {
         // ------------------------------- ring watcher -------------------------------
         if (lane == 0) {
-            // One arrival per phase of P_A's barrier: the next pair is often complete before the
-            // softmax threads are, so wait for the phase to end before arriving again.
+            // One arrival per phase of P_A's barrier: the next tiles are often there before the
+            // softmax threads are done, so wait for the phase to end before arriving again.
             for (int g = 0; g < n_tiles; g++) {
-                if (!mbar_wait(bar_full(g), (g >> 1) & 1, &abort_word)) break;
+                const int v = 2 * g + 1, k = 2 * g + 2;
+                if (!mbar_wait(bar_full(v % ST), (v / ST) & 1, &abort_word)) break;
+                if (g + 1 < n_tiles && !mbar_wait(bar_full(k % ST), (k / ST) & 1, &abort_word)) break;
                 mbar_arrive(bar_p_full(0));
                 if (!mbar_wait(bar_p_full(0), g & 1, &abort_word)) break;
             }

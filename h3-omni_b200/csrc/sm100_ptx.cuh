@@ -117,6 +117,26 @@ __device__ __forceinline__ bool mbar_wait_lane0(uint32_t bar, uint32_t parity, v
     return *abort_word == 0;
 }
 
+// For a converged warp whose lanes all wait for the same barrier: when the barrier is already
+// complete this is one probe per lane (one broadcast access for the warp) and nothing else;
+// otherwise every lane polls and the warp agrees on the outcome.
+__device__ __forceinline__ bool mbar_wait_converged(uint32_t bar, uint32_t parity, volatile int *abort_word) {
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_word));
+}
+
+// One lane of a converged warp (the predicate form the compiler recognises as "uniform code,
+// one lane acts": address arithmetic around it stays in the uniform datapath).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t chosen;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(chosen));
+    return chosen != 0;
+}
+
 // ---- TMA (non-multicast tile loads only) ---------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
