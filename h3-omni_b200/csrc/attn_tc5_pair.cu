@@ -328,12 +328,12 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 tmem_ld32(s_addr + 64, s2);
                 tmem_ld32(s_addr + 96, s3);
                 tmem_wait_ld();
-                float ma = -INFINITY, mb = -INFINITY;
-                max_chunk(s0, ma, mb);
-                max_chunk(s1, ma, mb);
-                max_chunk(s2, ma, mb);
-                max_chunk(s3, ma, mb);
-                const float m_new = fmaxf(m_ref, fmaxf(ma, mb));
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                max_chunk4(s0, mx);
+                max_chunk4(s1, mx);
+                max_chunk4(s2, mx);
+                max_chunk4(s3, mx);
+                const float m_new = fmaxf(max3(m_ref, mx[0], mx[1]), fmaxf(mx[2], mx[3]));
                 const bool grow = (m_new - m_ref) * p.scale_log2 > PAIR_RESCALE_LOG2;
                 if (__any_sync(0xffffffffu, grow)) {
                     const float alpha = grow ? fast_exp2((m_ref - m_new) * p.scale_log2) : 1.0f;

@@ -18,6 +18,16 @@ __device__ __forceinline__ void max_chunk(const uint32_t (&v)[32], float &m0, fl
         m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
     }
 }
+// The same over four independent chains (a lone warp on its scheduler is bound by the latency of
+// the chain, not by issue slots).
+__device__ __forceinline__ void max_chunk4(const uint32_t (&v)[32], float (&m)[4]) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            m[k] = max3(m[k], __uint_as_float(v[i + 2 * k]), __uint_as_float(v[i + 2 * k + 1]));
+    }
+}
 // Row maximum over a full tile. Loads of the next 32 columns are in flight while the
 // current 32 are reduced.
 template <int BN>
