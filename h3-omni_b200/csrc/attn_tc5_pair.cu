@@ -84,7 +84,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                      const PairParams p) {
     constexpr int ST = PAIR_STAGES;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[1 + 2 * ST + 5];
+    __shared__ uint64_t bars[1 + 2 * ST + 7];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_word;
 
@@ -99,8 +99,10 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     auto bar_full = [&](int s) { return bar0 + 8u * (1 + s); };
     auto bar_empty = [&](int s) { return bar0 + 8u * (1 + ST + s); };
     auto bar_s_full = [&](int t) { return bar0 + 8u * (1 + 2 * ST + t); };
-    auto bar_p_full = [&](int t) { return bar0 + 8u * (1 + 2 * ST + 2 + t); };
-    const uint32_t bar_pv_done = bar0 + 8u * (1 + 2 * ST + 4);   // the last PV of both tiles
+    // P is handed over in two halves of 64 keys so that the first four PV MMAs run while the
+    // exponentials of the second half are still being taken
+    auto bar_p_full = [&](int t, int half) { return bar0 + 8u * (1 + 2 * ST + 2 + 2 * t + half); };
+    const uint32_t bar_pv_done = bar0 + 8u * (1 + 2 * ST + 6);   // the last PV of both tiles
 
     const int head = blockIdx.y, batch = p.split_tiles ? 0 : blockIdx.z, out_batch = blockIdx.z;
     const int kv_head = head / (p.heads / p.kv_heads);
@@ -119,8 +121,10 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             mbar_init(bar_empty(s), 1);
         }
         for (int t = 0; t < 2; t++) mbar_init(bar_s_full(t), 1);
-        mbar_init(bar_p_full(0), 128 + 1);   // the softmax threads of tile A and the ring watcher
-        mbar_init(bar_p_full(1), 128);
+        mbar_init(bar_p_full(0, 0), 128 + 1);   // the softmax threads of tile A and the ring watcher
+        mbar_init(bar_p_full(0, 1), 128);
+        mbar_init(bar_p_full(1, 0), 128);
+        mbar_init(bar_p_full(1, 1), 128);
         mbar_init(bar_pv_done, 1);
         mbar_fence_init();
         abort_word = 0;
@@ -201,13 +205,15 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
                 __syncwarp();
             };
-            auto issue_pv = [&](int j, int t) {   // O_t += P_t . V_j
+            auto issue_pv = [&](int j, int t, int half) {   // O_t += P_t . V_j over 64 of the 128 keys
                 const uint32_t v_lo = v_ring_lo + ((2 * j + 1) % ST) * (PAIR_TILE_BYTES >> 4);
                 if (leader) {
 #pragma unroll
-                    for (int kk = 0; kk < PBN / 16; kk++)
+                    for (int k4 = 0; k4 < PBN / 32; k4++) {
+                        const int kk = half * (PBN / 32) + k4;
                         mma_ts_words(tmem + PAIR_O_COL + t * PHD, tmem + t * PBN + kk * 8,
                                      v_lo + kk * (2048 >> 4), v_hi, idesc_pv, (j > 0) || (kk > 0));
+                    }
                 }
                 __syncwarp();
             };
@@ -231,13 +237,16 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 {
                     // P of tile A, and (through the ring watcher) V of this step and K of the next
                     TRACE_T0();
-                    if (!mbar_wait_converged(bar_p_full(0), j & 1, &abort_word)) break;
+                    if (!mbar_wait_converged(bar_p_full(0, 0), j & 1, &abort_word)) break;
                     TRACE_ADD(0);
                 }
                 tc5_fence_after();
                 {
                     TRACE_T0();
-                    issue_pv(j, 0);
+                    issue_pv(j, 0, 0);
+                    if (!mbar_wait_converged(bar_p_full(0, 1), j & 1, &abort_word)) break;
+                    tc5_fence_after();
+                    issue_pv(j, 0, 1);
                     TRACE_ADD(4);
                 }
                 if (more) {
@@ -247,11 +256,14 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
                 {
                     TRACE_T0();
-                    if (!mbar_wait_converged(bar_p_full(1), j & 1, &abort_word)) break;
+                    if (!mbar_wait_converged(bar_p_full(1, 0), j & 1, &abort_word)) break;
                     TRACE_ADD(3);
                 }
                 tc5_fence_after();
-                issue_pv(j, 1);
+                issue_pv(j, 1, 0);
+                if (!mbar_wait_converged(bar_p_full(1, 1), j & 1, &abort_word)) break;
+                tc5_fence_after();
+                issue_pv(j, 1, 1);
                 release(2 * j + 1);
                 if (more) {
                     issue_qk(j + 1, 1);
@@ -283,8 +295,8 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 const int v = 2 * g + 1, k = 2 * g + 2;
                 if (!mbar_wait(bar_full(v % ST), (v / ST) & 1, &abort_word)) break;
                 if (g + 1 < n_tiles && !mbar_wait(bar_full(k % ST), (k / ST) & 1, &abort_word)) break;
-                mbar_arrive(bar_p_full(0));
-                if (!mbar_wait(bar_p_full(0), g & 1, &abort_word)) break;
+                mbar_arrive(bar_p_full(0, 0));
+                if (!mbar_wait(bar_p_full(0, 0), g & 1, &abort_word)) break;
             }
         }
     }
@@ -320,6 +332,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #ifdef H3B_TRACE
             const long long trace_work = clock64();
 #endif
+            bool first_half_out = false;
             if (nvalid >= PBN) {
                 // the whole row of scores in registers: one TMEM read pass
                 uint32_t s0[32], s1[32], s2[32], s3[32];
@@ -362,6 +375,10 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 tmem_st16(s_addr, packed);
                 exp_chunk_mixed<PAIR_POLY_EVERY>(s1, packed, scale2, neg2, sum0, sum1);
                 tmem_st16(s_addr + 16, packed);
+                tmem_wait_st();
+                tc5_fence_before();
+                mbar_arrive(bar_p_full(t, 0));
+                first_half_out = true;
                 exp_chunk_mixed<PAIR_POLY_EVERY>(s2, packed, scale2, neg2, sum0, sum1);
                 tmem_st16(s_addr + 32, packed);
                 exp_chunk_mixed<PAIR_POLY_EVERY>(s3, packed, scale2, neg2, sum0, sum1);
@@ -394,7 +411,8 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             }
             tmem_wait_st();
             tc5_fence_before();
-            mbar_arrive(bar_p_full(t));
+            if (!first_half_out) mbar_arrive(bar_p_full(t, 0));
+            mbar_arrive(bar_p_full(t, 1));
 #ifdef H3B_TRACE
             g_pair_trace_local[1] += clock64() - trace_work;
 #endif
