@@ -92,6 +92,9 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_smem = smem_base;
     const uint32_t ring = q_smem + PAIR_Q_BYTES;
+    // A launch whose stream has already recorded a failure does nothing: when a protocol error
+    // makes every CTA run into its wait limit, the CTAs that have not started yet leave at once.
+    if (*reinterpret_cast<volatile int *>(p.status) != STATUS_OK) return;
 
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t bar_q_full = bar0;
