@@ -87,14 +87,12 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     __shared__ uint64_t bars[1 + 2 * ST + 7];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_word;
+    __shared__ int skip_launch;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_smem = smem_base;
     const uint32_t ring = q_smem + PAIR_Q_BYTES;
-    // A launch whose stream has already recorded a failure does nothing: when a protocol error
-    // makes every CTA run into its wait limit, the CTAs that have not started yet leave at once.
-    if (*reinterpret_cast<volatile int *>(p.status) != STATUS_OK) return;
 
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t bar_q_full = bar0;
@@ -131,6 +129,9 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         mbar_init(bar_pv_done, 1);
         mbar_fence_init();
         abort_word = 0;
+        // A launch whose stream has already recorded a failure does nothing: when a protocol
+        // error makes every CTA run into its wait limit, the CTAs that start later leave at once.
+        skip_launch = *reinterpret_cast<volatile int *>(p.status) != STATUS_OK;
     }
     if (warp == 9) {
         tmem_alloc(smem_u32(&tmem_slot), 512);
@@ -141,7 +142,9 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     tc5_fence_after();
     const uint32_t tmem = tmem_slot;
 
-    if (warp >= 8) {
+    if (skip_launch) {
+        // straight to the teardown
+    } else if (warp >= 8) {
     warpgroup_reg_dec<88>();
     if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
