@@ -353,8 +353,12 @@ attn_sparse_t_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
             }
             TR_OUT(0, 1);
-        } else if (warp == 9 && lane == 0) {
+        } else if (warp == 9) {
             // ------------------------------ QK issue: S^T[g & 1] = K pair . Q^T ------------------------------
+            // The whole warp walks the loop and one elected lane issues: inside a one-lane branch
+            // every descriptor word would be per-thread data that has to be moved to a uniform
+            // register in front of each MMA.
+            const bool leader = elect_one();
             constexpr uint32_t idesc_qk = idesc_bf16(128, 64, 0, 0);
             const uint64_t q_proto = smem_desc_sw128(base + ST_OFF_Q, 16, 1024);
             const uint64_t k_proto = smem_desc_sw128(base + ST_OFF_RING, 16, 1024);
@@ -364,31 +368,34 @@ attn_sparse_t_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             TR_DECL;
             for (int i = 0;; i++) {
                 Item it;
-                if (!fetch(i, it) || it.n < 0) break;
+                if (!fetch_warp(i, it) || it.n < 0) break;
                 if (it.n == 0) continue;
                 int &uses = (i & 1) ? q_uses1 : q_uses0;   // only items with a list load a query tile
-                if (!mbar_wait(bar_q_full(i & 1), (uses++) & 1, &abort_word)) break;
+                if (!mbar_wait_converged(bar_q_full(i & 1), (uses++) & 1, &abort_word)) break;
                 const uint32_t b_lo = q_lo0 + (i & 1) * (ST_Q >> 4);
                 bool ok = true;
                 for (int j = 0; j < it.n; j++, g++) {
                     const int slot = g & 1;
                     {
                         TR_T0;
-                        ok = mbar_wait(bar_k_full(slot), (g >> 1) & 1, &abort_word) &&
+                        ok = mbar_wait_converged(bar_k_full(slot), (g >> 1) & 1, &abort_word) &&
                              // the softmax group has finished reading S^T of step g - 2
-                             (g < 2 || mbar_wait(bar_p_full(slot), ((g - 2) >> 1) & 1, &abort_word));
+                             (g < 2 || mbar_wait_converged(bar_p_full(slot), ((g - 2) >> 1) & 1, &abort_word));
                         TR_ADD(0);
                     }
                     if (!ok) break;
                     TR_T0;
                     tc5_fence_after();
                     const uint32_t a_lo = k_lo0 + slot * (ST_SLOT >> 4), d_tmem = tmem + ST_S_COL + slot * 64;
+                    if (leader) {
 #pragma unroll
-                    for (int kk = 0; kk < 8; kk++)
-                        mma_ss_words(d_tmem, a_lo + (kk / 4) * (ST_HALF >> 4) + (kk % 4) * 2, k_hi,
-                                     b_lo + (kk / 4) * (ST_QHALF >> 4) + (kk % 4) * 2, q_hi, idesc_qk, kk > 0);
-                    mma_commit(bar_s_full(slot));
-                    mma_commit(bar_k_empty(slot));
+                        for (int kk = 0; kk < 8; kk++)
+                            mma_ss_words(d_tmem, a_lo + (kk / 4) * (ST_HALF >> 4) + (kk % 4) * 2, k_hi,
+                                         b_lo + (kk / 4) * (ST_QHALF >> 4) + (kk % 4) * 2, q_hi, idesc_qk, kk > 0);
+                        mma_commit(bar_s_full(slot));
+                        mma_commit(bar_k_empty(slot));
+                    }
+                    __syncwarp();
                     TR_ADD(1);
                 }
                 if (!ok) break;
@@ -396,9 +403,10 @@ attn_sparse_t_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #ifdef H3B_TRACE
             tr_acc[2] = g;
 #endif
-            TR_OUT(8, 3);
-        } else if (warp == 11 && lane == 0) {
+            if (lane == 0) TR_OUT(8, 3);
+        } else if (warp == 11) {
             // ------------------------------ PV issue: O^T[item & 1] += V pair^T . P^T[g & 1] ------------------------------
+            const bool leader = elect_one();
             constexpr uint32_t idesc_pv = idesc_bf16(128, 64, 1, 1);
             const uint64_t v_proto = smem_desc_sw128(base + ST_OFF_RING + 2 * ST_SLOT, ST_HALF, 1024);
             const uint64_t p_proto = smem_desc_sw128(base + ST_OFF_P, ST_P, 1024);
@@ -409,11 +417,12 @@ attn_sparse_t_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             for (int i = 0;; i++) {
                 Item it;
                 const int b = i & 1;
-                if (!fetch(i, it) || it.n < 0) break;
+                if (!fetch_warp(i, it) || it.n < 0) break;
                 // the accumulator (and the item_done phase) of item i - 2 must have been consumed
-                if (i >= 2 && !mbar_wait(bar_item_free(b), ((i >> 1) - 1) & 1, &abort_word)) break;
+                if (i >= 2 && !mbar_wait_converged(bar_item_free(b), ((i >> 1) - 1) & 1, &abort_word)) break;
                 if (it.n == 0) {   // empty list: nothing to multiply; the epilogue writes zero rows
-                    mbar_arrive(bar_item_done(b));
+                    if (leader) mbar_arrive(bar_item_done(b));
+                    __syncwarp();
                     continue;
                 }
                 const uint32_t d_tmem = tmem + ST_O_COL + b * 64;
@@ -422,32 +431,36 @@ attn_sparse_t_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     const int slot = g & 1;
                     {
                         TR_T0;
-                        ok = mbar_wait(bar_v_full(slot), (g >> 1) & 1, &abort_word) &&
-                             mbar_wait(bar_p_full(slot), (g >> 1) & 1, &abort_word);
+                        ok = mbar_wait_converged(bar_v_full(slot), (g >> 1) & 1, &abort_word) &&
+                             mbar_wait_converged(bar_p_full(slot), (g >> 1) & 1, &abort_word);
                         TR_ADD(0);
                     }
                     if (!ok) break;
                     TR_T0;
                     tc5_fence_after();
                     const uint32_t a_lo = v_lo0 + slot * (ST_SLOT >> 4), b_lo = p_lo0 + slot * (ST_P >> 4);
-                    mma_ss_words(d_tmem, a_lo, v_hi, b_lo, p_hi, idesc_pv, j > 0);
+                    if (leader) {
+                        mma_ss_words(d_tmem, a_lo, v_hi, b_lo, p_hi, idesc_pv, j > 0);
 #pragma unroll
-                    for (int kk = 1; kk < 4; kk++)
-                        mma_ss_words(d_tmem, a_lo + kk * (2048 >> 4), v_hi, b_lo + kk * (2048 >> 4), p_hi, idesc_pv, 1);
-                    if (!single(it, j)) {   // never multiply rows of a tile that was not loaded
+                        for (int kk = 1; kk < 4; kk++)
+                            mma_ss_words(d_tmem, a_lo + kk * (2048 >> 4), v_hi, b_lo + kk * (2048 >> 4), p_hi, idesc_pv, 1);
+                        if (!single(it, j)) {   // never multiply rows of a tile that was not loaded
 #pragma unroll
-                        for (int kk = 4; kk < 8; kk++)
-                            mma_ss_words(d_tmem, a_lo + kk * (2048 >> 4), v_hi, b_lo + kk * (2048 >> 4), p_hi,
-                                         idesc_pv, 1);
+                            for (int kk = 4; kk < 8; kk++)
+                                mma_ss_words(d_tmem, a_lo + kk * (2048 >> 4), v_hi, b_lo + kk * (2048 >> 4), p_hi,
+                                             idesc_pv, 1);
+                        }
+                        mma_commit(bar_v_empty(slot));
+                        mma_commit(bar_pv_done(slot));
                     }
-                    mma_commit(bar_v_empty(slot));
-                    mma_commit(bar_pv_done(slot));
+                    __syncwarp();
                     TR_ADD(1);
                 }
                 if (!ok) break;
-                mma_commit(bar_item_done(b));
+                if (leader) mma_commit(bar_item_done(b));
+                __syncwarp();
             }
-            TR_OUT(12, 2);
+            if (lane == 0) TR_OUT(12, 2);
         }
     } else if (warp >= 12) {
         warpgroup_reg_dec<64>();

@@ -108,30 +108,37 @@ out_proj_gate_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             }
         }
     } else if (warp == 5) {
-        if (lane == 0) {
+        // The whole warp walks the loop and one elected lane issues (descriptor arithmetic stays
+        // in the uniform datapath; inside a one-lane branch it would be per-thread data).
+        {
+            const bool leader = elect_one();
             constexpr uint32_t idesc = mma_idesc(GM, GN, 1, 0);
             const uint64_t a_proto = smem_desc_sw128(base, 16, 1024), b_proto = smem_desc_sw128(base + G_A_BYTES, 16, 1024);
             const uint32_t a_lo0 = (uint32_t)a_proto, hi = (uint32_t)(a_proto >> 32), b_lo0 = (uint32_t)b_proto;
             int fill = 0, local = 0;
             for (int tile = blockIdx.x; tile < total; tile += gridDim.x, local++) {
                 const int acc = local & 1;
-                bool ok = local < 2 || mbar_wait(bar_acc_empty(acc), ((local >> 1) - 1) & 1, &abort_word);
+                bool ok = local < 2 || mbar_wait_converged(bar_acc_empty(acc), ((local >> 1) - 1) & 1, &abort_word);
                 tc5_fence_after();
                 for (int k = 0; ok && k < ksteps; k++, fill++) {
                     const int s = fill % G_STAGES;
-                    if (!mbar_wait(bar_full(s), (fill / G_STAGES) & 1, &abort_word)) {
+                    if (!mbar_wait_converged(bar_full(s), (fill / G_STAGES) & 1, &abort_word)) {
                         ok = false;
                         break;
                     }
                     tc5_fence_after();
                     const uint32_t a_lo = a_lo0 + s * (G_STAGE >> 4), b_lo = b_lo0 + s * (G_STAGE >> 4);
+                    if (leader) {
 #pragma unroll
-                    for (int kk = 0; kk < GK / 16; kk++)
-                        mma_ss_words(tmem + acc * GN, a_lo + kk * 2, hi, b_lo + kk * 2, hi, idesc, (k > 0) || (kk > 0));
-                    mma_commit(bar_empty(s));
+                        for (int kk = 0; kk < GK / 16; kk++)
+                            mma_ss_words(tmem + acc * GN, a_lo + kk * 2, hi, b_lo + kk * 2, hi, idesc, (k > 0) || (kk > 0));
+                        mma_commit(bar_empty(s));
+                    }
+                    __syncwarp();
                 }
                 if (!ok) break;
-                mma_commit(bar_acc_full(acc));
+                if (leader) mma_commit(bar_acc_full(acc));
+                __syncwarp();
             }
         }
     } else {
