@@ -31,7 +31,7 @@ SEQ_VIDEO, SEQ_AUDIO, HEADS, DIM = 51840, 512, 24, 128
 SEQ = SEQ_VIDEO + SEQ_AUDIO
 SCALE = float(1.0 / np.sqrt(128.0))
 EXCHANGE_NOTE = "fused peer-memory push kernels; gather fused into the attention epilogue"
-E2E_HEAD_GROUPS = int(os.environ.get("H3B_E2E_GROUPS", "6"))   # head groups of the pipelined host-buffer call (4 heads each at H=24)
+E2E_HEAD_GROUPS = int(os.environ.get("H3B_E2E_GROUPS", "0"))   # head groups of the pipelined host-buffer call; 0: the library plans the chunks
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dense kernel, measured by ncu at
 # L=16,384, H=24: 384.8 MB (algorithmic 402.7 MB; part of the output was still in L2 at kernel
 # end). Traffic grows with L*H, so per row of one head:
@@ -306,6 +306,11 @@ def main():
     pipe = HostPipeline(env, exchange, slots, rows, (host_q, host_k, host_v), host_o) \
         if exchange is not None and HEADS % (3 * world) == 0 else None
 
+    # the head counts of the chunks the host-buffer call runs as (one kernel launch each)
+    chunk_heads = (C.c_uint32 * 66)()
+    lib.h3b_sdpa_host_plan.restype = C.c_uint32
+    e2e_chunks = list(chunk_heads[:lib.h3b_sdpa_host_plan(SEQ, HEADS, E2E_HEAD_GROUPS, chunk_heads, 66)])
+
     def e2e_step():
         """The same step through the public API with host buffers."""
         if world == 1:
@@ -313,7 +318,7 @@ def main():
             if not lib.h3b_sdpa_bf16_host(gpu.gpu, host_o.data_ptr(), host_q.data_ptr(), host_k.data_ptr(),
                                           host_v.data_ptr(), SEQ, HEADS, DIM, SCALE, E2E_HEAD_GROUPS):
                 raise RuntimeError(gpu.error())
-            launches[0] += E2E_HEAD_GROUPS + (2 if HEADS // E2E_HEAD_GROUPS >= 2 else 0)   # edge groups run as two halves
+            launches[0] += len(e2e_chunks)
             return
         if pipe is not None:
             pipe.step()
@@ -412,7 +417,7 @@ def main():
         "roofline": roofline,
         "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": 3 * shard_elems * 2, "d2h_bytes_per_step": shard_elems * 2,
-                "api": "h3b_sdpa_bf16_host (pinned host buffers, %d pipelined head groups)" % E2E_HEAD_GROUPS
+                "api": "h3b_sdpa_bf16_host (pinned host buffers, pipelined head chunks %s)" % " ".join(map(str, e2e_chunks))
                        if world == 1 else
                        ("pinned host shards, 3 head groups pipelined: 2-D copy-in | fused scatter + attention with "
                         "fused gather | copy-out" if pipe is not None else

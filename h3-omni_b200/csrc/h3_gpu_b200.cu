@@ -437,6 +437,59 @@ static int pipeline_prepare(h3_gpu *g, size_t slot_bytes) {
     p.ready = true;
     return 1;
 }
+// How the heads of a host-buffer call are cut into chunks that run back to back. The copy-in
+// before the first kernel and the copy-out after the last one are the only transfers nothing
+// overlaps, so the first and the last chunk are short. head_groups > 0: equal groups, the two
+// outer ones halved. head_groups == 0: the outer chunks are two heads and the inner chunk size is
+// the one that wastes the fewest CTA waves (a chunk of n heads launches n * ceil(sequence / 256)
+// CTAs on `sms` SMs, and its last wave is partly empty), ties going to the smaller chunk.
+extern "C" uint32_t h3b_sdpa_host_plan(uint32_t sequence, uint32_t heads, uint32_t head_groups, uint32_t *head_count,
+                                       uint32_t capacity) {
+    uint32_t chunks = 0;
+    auto push = [&](uint32_t n) {
+        if (n && chunks < capacity) head_count[chunks] = n;
+        chunks += n ? 1 : 0;
+    };
+    if (!heads || !sequence) return 0;
+    if (head_groups) {
+        if (heads % head_groups || head_groups > 64) return 0;
+        const uint32_t hg = heads / head_groups;
+        for (uint32_t group = 0; group < head_groups; group++) {
+            const bool edge = (group == 0 || group + 1 == head_groups) && hg >= 2;
+            if (edge) {
+                push(hg / 2);
+                push(hg - hg / 2);
+            } else {
+                push(hg);
+            }
+        }
+    } else {
+        int device = 0, sms = 148;
+        if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        const uint64_t per_head = (sequence + 255) / 256;
+        auto waves = [&](uint32_t n) { return (n * per_head + sms - 1) / sms; };
+        const uint32_t edge = heads >= 8 ? 2 : heads >= 4 ? 1 : 0, inner = heads - 2 * edge;
+        uint32_t best = 1;
+        uint64_t best_waves = ~0ull;
+        for (uint32_t c = 1; c <= 8 && c <= inner; c++) {
+            const uint32_t n = (inner + c - 1) / c, small = n * c - inner;   // `small` chunks hold c - 1 heads
+            if (small > n || (c == 1 && small)) continue;
+            const uint64_t w = (n - small) * waves(c) + small * waves(c - 1);
+            if (w < best_waves) {
+                best_waves = w;
+                best = c;
+            }
+        }
+        push(edge);
+        if (inner) {
+            const uint32_t n = (inner + best - 1) / best, small = n * best - inner;
+            for (uint32_t i = 0; i < n; i++) push(i < n - small ? best : best - 1);
+        }
+        push(edge);
+    }
+    return chunks <= capacity ? chunks : 0;
+}
+
 extern "C" int h3b_sdpa_bf16_host(h3_gpu *g, uint16_t *out, const uint16_t *q, const uint16_t *k,
                                   const uint16_t *v, uint32_t sequence, uint32_t heads,
                                   uint32_t head_dim, float scale, uint32_t head_groups) {
@@ -449,30 +502,20 @@ extern "C" int h3b_sdpa_bf16_host(h3_gpu *g, uint16_t *out, const uint16_t *q, c
         fail(g, "BF16 attention supports head dimension 128 only");
         return 0;
     }
-    if (!head_groups || heads % head_groups) {
-        fail(g, "host attention: %u heads do not split into %u groups", heads, head_groups);
-        return 0;
-    }
-    const uint32_t hg = heads / head_groups;
-    const size_t pitch = (size_t)heads * 256;
-    if (!pipeline_prepare(g, (size_t)hg * 256 * sequence)) return 0;
-    host_pipeline &p = g->pipe;
-    // The first and the last group are cut in two: the copy-in before the first kernel and the
-    // copy-out after the last one are the only transfers nothing overlaps, so they are made short.
     uint32_t first_head[66], head_count[66];
-    uint32_t chunks = 0;
-    if (head_groups > 64) {
-        fail(g, "host attention: at most 64 head groups");
+    const uint32_t chunks = h3b_sdpa_host_plan(sequence, heads, head_groups, head_count, 66);
+    if (!chunks) {
+        fail(g, "host attention: %u heads do not split into %u groups (at most 64)", heads, head_groups);
         return 0;
     }
-    for (uint32_t group = 0; group < head_groups; group++) {
-        const bool edge = (group == 0 || group + 1 == head_groups) && hg >= 2;
-        const uint32_t parts = edge ? 2 : 1, base = group * hg;
-        for (uint32_t part = 0; part < parts; part++) {
-            first_head[chunks] = base + (part ? hg / 2 : 0);
-            head_count[chunks++] = parts == 1 ? hg : part ? hg - hg / 2 : hg / 2;
-        }
+    uint32_t widest = 0;
+    for (uint32_t c = 0, at = 0; c < chunks; at += head_count[c++]) {
+        first_head[c] = at;
+        widest = head_count[c] > widest ? head_count[c] : widest;
     }
+    const size_t pitch = (size_t)heads * 256;
+    if (!pipeline_prepare(g, (size_t)widest * 256 * sequence)) return 0;
+    host_pipeline &p = g->pipe;
     // everything already queued on the context's stream comes first
     if (!cuda_good(g, cudaEventRecord(p.computed[0], g->stream)) ||
         !cuda_good(g, cudaStreamWaitEvent(p.h2d, p.computed[0], 0)))

@@ -256,11 +256,16 @@ int h3b_attention_output_gate_adaln_bf16(
 
 /* Dense attention from and to HOST memory, head dim 128: q, k, v, out are token-major
  * [sequence][heads][128] bf16 in host memory (pinned for full speed). The heads are cut into
- * head_groups groups (heads % head_groups == 0) and copy-in, kernel and copy-out of
- * consecutive groups overlap on three streams, so the call costs about
- * max(copy time, kernel time); the first and the last group run as two halves to shorten the
- * two transfers nothing can overlap. head_groups <= 64. Synchronous: returns when `out` is
- * complete. */
+ * chunks, and copy-in, kernel and copy-out of consecutive chunks overlap on three streams, so the
+ * call costs about max(copy time, kernel time). head_groups > 0: that many equal groups
+ * (heads % head_groups == 0, at most 64), the first and the last run as two halves to shorten the
+ * two transfers nothing can overlap. head_groups == 0: the library chooses - outer chunks of two
+ * heads, inner chunks of the size whose kernel launches waste the fewest CTA waves on this GPU
+ * (24 heads of 52,352 rows on 148 SMs: 2 5 5 5 5 2). Synchronous: returns when `out` is complete.
+ * h3b_sdpa_host_plan returns the number of chunks such a call uses and writes their head counts
+ * (0: the heads do not split that way, or more than `capacity` chunks). */
+uint32_t h3b_sdpa_host_plan(uint32_t sequence, uint32_t heads, uint32_t head_groups, uint32_t *head_count,
+                            uint32_t capacity);
 int h3b_sdpa_bf16_host(h3_gpu *gpu, uint16_t *out, const uint16_t *q, const uint16_t *k,
                        const uint16_t *v, uint32_t sequence, uint32_t heads, uint32_t head_dim,
                        float scale, uint32_t head_groups);

@@ -55,3 +55,24 @@ def test_calls_without_a_context_fail_cleanly(library):
     assert lib.h3b_comm_rank(None) == -1 and lib.h3b_comm_size(None) == 0
     assert lib.h3_gpu_tensor_elements(None) == 0
     assert C.string_at(lib.h3_gpu_error(None)) == b"no GPU context"
+
+
+def test_host_call_plans_its_head_chunks(library):
+    """h3b_sdpa_host_plan is host arithmetic (no GPU: it assumes 148 SMs when no device answers):
+    equal groups with the outer two halved, or, asked to choose, outer chunks of two heads and the
+    inner chunk size that wastes the fewest CTA waves - five heads of 205 CTAs fill 6.93 waves."""
+    _, lib = library
+    lib.h3b_sdpa_host_plan.restype = C.c_uint32
+    counts = (C.c_uint32 * 66)()
+
+    def plan(sequence, heads, groups, capacity=66):
+        return list(counts[:lib.h3b_sdpa_host_plan(sequence, heads, groups, counts, capacity)])
+
+    assert plan(52352, 24, 6) == [2, 2, 4, 4, 4, 4, 2, 2]
+    assert plan(52352, 24, 0) == [2, 5, 5, 5, 5, 2]
+    assert plan(700, 8, 1) == [4, 4] and plan(700, 8, 4) == [1, 1, 2, 2, 1, 1]
+    assert plan(700, 8, 3) == [] and plan(700, 0, 0) == [] and plan(52352, 24, 6, capacity=4) == []
+    for heads in range(1, 65):
+        for sequence in (1, 700, 16384, 101464):
+            chunks = plan(sequence, heads, 0)
+            assert sum(chunks) == heads and all(chunks), (heads, sequence, chunks)

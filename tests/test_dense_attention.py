@@ -252,7 +252,7 @@ def test_run_twice_is_deterministic(gpu, oracle):
     assert np.array_equal(outs[0], outs[1])
 
 
-@pytest.mark.parametrize("groups", [1, 2, 4])
+@pytest.mark.parametrize("groups", [0, 1, 2, 4])
 def test_host_buffer_attention_matches_device_path(gpu, oracle, groups):
     """h3b_sdpa_bf16_host (head groups pipelined over copy and compute streams, pageable host
     memory here) gives the same bits as the device-tensor primitive: grouping heads changes
