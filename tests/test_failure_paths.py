@@ -135,3 +135,39 @@ def test_submit_refuses_a_context_of_another_device(gpu):
         assert "is current" in gpu.error()
     finally:
         assert gpu.lib.h3_gpu_select_device(0, err, 256), err.value
+
+
+def test_launches_after_a_recorded_failure_do_nothing_until_it_is_reported(gpu, oracle):
+    """Once the device status word holds a failure, the dense attention kernel's CTAs leave at
+    once (so a protocol error cannot make thousands of CTAs run into their wait limits one wave
+    after the other): the output keeps what was in it. The failure is reported by the next submit,
+    which clears the word, and the same launch then computes."""
+    d = gpu.lib.h3b_tensor_data
+    stream = gpu.lib.h3b_gpu_stream(gpu.gpu)
+    # a refused index list (a count beyond the number of tiles) records status 2 without any fault
+    tiles, heads = 4, 1
+    fq, fk, fv = (oracle.normal_bf16((heads, tiles * 64, 128), 70 + i) for i in range(3))
+    indices = np.tile(np.arange(tiles, dtype=np.int32), (heads, tiles, 1))
+    counts = np.full((heads, tiles), tiles + 1, dtype=np.int32)
+    sizes = np.full(tiles, 64, dtype=np.int32)
+    ft = [gpu.tensor(x) for x in (fq, fk, fv, indices, counts, sizes)]
+    fo = gpu.empty_bf16(fq.size)
+    gpu.raw("h3_vsa_hopper", d(fo), d(ft[0]), d(ft[1]), d(ft[2]), None, d(ft[3]), d(ft[4]), d(ft[5]), tiles, heads,
+            stream)
+    # dense attention with more than one query tile, into an output that holds a marker
+    L, H = 300, 2
+    q, k, v = (oracle.normal_bf16((1, L, H, 128), 80 + i) for i in range(3))
+    tq, tk, tv = gpu.tensor(q), gpu.tensor(k), gpu.tensor(v)
+    marker = np.full(q.shape, 0x1234, dtype=np.uint16)
+    ty = gpu.tensor(marker)
+    scale = C.c_float(float(1 / np.sqrt(128)))
+    gpu.raw("h3_flash3_bf16", d(ty), d(tq), d(tk), d(tv), None, 1, L, H, H, scale, stream)
+    assert not gpu.lib.h3_gpu_submit(gpu.gpu)
+    assert "bounds check failed" in gpu.error()
+    assert gpu.lib.h3_gpu_submit(gpu.gpu), gpu.error()
+    assert np.array_equal(gpu.read(ty, q.shape), marker)
+    gpu.raw("h3_flash3_bf16", d(ty), d(tq), d(tk), d(tv), None, 1, L, H, H, scale, stream)
+    want, _ = oracle.attention(q, k, v, float(1 / np.sqrt(128)))
+    assert np.abs(oracle.from_bf16(gpu.read(ty, q.shape)) - want).max() <= 1e-2
+    for t in ft + [fo, tq, tk, tv, ty]:
+        gpu.free(t)
