@@ -163,7 +163,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 for (int tile = 0; ok && tile < tiles; tile++) {
                     for (int which = 0; which < 2; which++, idx++) {
                         const int s = idx % ST, use = idx / ST;
-                        if (use > 0 && !mbar_wait(bar_empty(s), (use - 1) & 1, &abort_word)) {
+                        if (use > 0 && !mbar_wait_parked(bar_empty(s), (use - 1) & 1, &abort_word)) {
                             ok = false;
                             break;
                         }
@@ -299,10 +299,10 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             // softmax threads are done, so wait for the phase to end before arriving again.
             for (int g = 0; g < n_tiles; g++) {
                 const int v = 2 * g + 1, k = 2 * g + 2;
-                if (!mbar_wait(bar_full(v % ST), (v / ST) & 1, &abort_word)) break;
-                if (g + 1 < n_tiles && !mbar_wait(bar_full(k % ST), (k / ST) & 1, &abort_word)) break;
+                if (!mbar_wait_parked(bar_full(v % ST), (v / ST) & 1, &abort_word)) break;
+                if (g + 1 < n_tiles && !mbar_wait_parked(bar_full(k % ST), (k / ST) & 1, &abort_word)) break;
                 mbar_arrive(bar_p_full(0, 0));
-                if (!mbar_wait(bar_p_full(0, 0), g & 1, &abort_word)) break;
+                if (!mbar_wait_parked(bar_p_full(0, 0), g & 1, &abort_word)) break;
             }
         }
     }
@@ -330,7 +330,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             seg_tile++;
             {
                 TRACE_T0();
-                alive = __all_sync(0xffffffffu, mbar_wait(bar_s_full(t), j & 1, &abort_word));
+                alive = __all_sync(0xffffffffu, mbar_wait_parked(bar_s_full(t), j & 1, &abort_word));
                 TRACE_ADD(0);
             }
             if (!alive) break;

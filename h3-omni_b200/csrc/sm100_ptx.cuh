@@ -58,6 +58,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
+// The same probe with a suspend-time hint: a probe that finds the phase incomplete parks the
+// thread in hardware for up to `ns` nanoseconds (or until the phase completes) instead of coming
+// straight back, so a long wait costs a few probes, not thousands of loop iterations.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait for waits that are expected to be long (a softmax thread waiting for its next
+// score tile, the producer waiting for a free slot): parked probes.
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int *abort_word) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long start = global_timer_ns();
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait_parked(bar, parity, 4000u)) return true;
+        if ((spin & 15u) == 0u) {
+            if (*abort_word) return false;
+            if (global_timer_ns() - start > WAIT_LIMIT_NS) {
+                *abort_word = 1;
+                return false;
+            }
+        }
+    }
+}
+
 // Bounded wait. Returns false when the CTA is aborting (this waiter or another
 // one ran out of time); `abort_word` lives in shared memory.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_word) {
