@@ -7,7 +7,7 @@
 //      PV_A(j)  QK_A(j+1)  PV_B(j)  QK_B(j+1)  ...
 // so that while softmax warpgroup A works on S_A(j+1) the tensor pipe runs B's MMAs and vice
 // versa. One CTA per SM: all 512 TMEM columns (S_A, S_B, O_A, O_B, 128 each), 64 KB of Q and a
-// four-stage K/V ring in shared memory.
+// five-slot K/V ring in shared memory.
 //   warps 0-3 / 4-7 : softmax warpgroups A / B (one thread per query row, the row's 128
 //                     scores held in registers: one TMEM read pass)
 //   warp 8          : TMA producer
@@ -22,6 +22,9 @@
 // S(j) also covers PV(j-1), issued before it by the same thread. The ring has five slots: a tile
 // takes 2000-3000 cycles from the request to shared memory when every SM asks at once, and with
 // four slots (two steps of K/V) the request for step j+2 cannot leave before step j is over.
+// P goes to the issuer in two halves of 64 keys, so the first four PV MMAs of a tile run while the
+// second half of its exponentials is still being taken; waits that are expected to be long park
+// in hardware (mbar_wait_parked) - at the board's power limit a spinning warp costs clock.
 // A fixed fraction of the exponentials is evaluated by a polynomial on the FMA pipe (see
 // softmax_tc5.cuh) so the exponential unit is not the critical resource.
 // Serves h3_flash3_bf16 / h3_flash3_cross_bf16 / non-causal h3_flash_bf16 whenever the call
