@@ -46,7 +46,7 @@ constexpr int PAIR_Q_BYTES = 2 * PBM * PHD * 2;     // 64 KB
 constexpr int PAIR_SMEM_BYTES = PAIR_Q_BYTES + PAIR_STAGES * PAIR_TILE_BYTES + 1024;
 constexpr int PAIR_O_COL = 256;
 constexpr float PAIR_RESCALE_LOG2 = 8.0f;
-constexpr int PAIR_POLY_EVERY = 2;                  // 25 % of the exponentials on the FMA pipe
+constexpr int PAIR_POLY_EVERY = 0x55;               // which groups of four columns take a pair of exponentials on the FMA pipe (25 %)
 
 #ifdef H3B_TRACE
 // Development aid, compiled only with -DH3B_TRACE: cycle counters of CTA (0,0,0).
@@ -269,14 +269,20 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     TRACE_ADD(3);
                 }
                 tc5_fence_after();
-                issue_pv(j, 1, 0);
-                if (!mbar_wait_converged(bar_p_full(1, 1), j & 1, &abort_word)) break;
-                tc5_fence_after();
-                issue_pv(j, 1, 1);
-                release(2 * j + 1);
+                {
+                    TRACE_T0();
+                    issue_pv(j, 1, 0);
+                    if (!mbar_wait_converged(bar_p_full(1, 1), j & 1, &abort_word)) break;
+                    tc5_fence_after();
+                    issue_pv(j, 1, 1);
+                    release(2 * j + 1);
+                    TRACE_ADD(6);
+                }
                 if (more) {
+                    TRACE_T0();
                     issue_qk(j + 1, 1);
                     release(2 * j + 2);
+                    TRACE_ADD(7);
                 } else if (leader) {
                     mma_commit(bar_pv_done);      // both accumulators are final
                 }
@@ -292,6 +298,8 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 g_pair_trace[5] = n_tiles;
                 g_pair_trace[6] = g_pair_trace_local[4];     // thread time inside issue_pv(A)
                 g_pair_trace[7] = g_pair_trace_local[5];     // thread time inside issue_qk(A)
+                g_pair_trace[24] = g_pair_trace_local[6];    // the same for tile B: both PV halves with the wait between them
+                g_pair_trace[25] = g_pair_trace_local[7];    // issue_qk(B) and the ring release
             }
 #endif
         }

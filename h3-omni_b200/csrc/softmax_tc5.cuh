@@ -161,9 +161,10 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
     r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
     return r;
 }
-// exp_chunk where, in every POLY_EVERY-th group of four columns, the second pair is evaluated
-// by exp2_poly2: POLY_EVERY = 1 -> 50 % of the columns, 2 -> 25 %, 4 -> 12.5 %, 0 -> none.
-template <int POLY_EVERY>
+// exp_chunk where, in the groups of four columns named by POLY_MASK (bit g = group g of the
+// chunk's eight), the second pair is evaluated by exp2_poly2: 0x55 -> 25 % of the columns,
+// 0x6d -> 31 %, 0xff -> 50 %, 0 -> none.
+template <int POLY_MASK>
 __device__ __forceinline__ void exp_chunk_mixed(const uint32_t (&v)[32], uint32_t (&packed)[16],
                                                 float2 scale2, float2 neg2, float2 &sum0,
                                                 float2 &sum1) {
@@ -174,7 +175,7 @@ __device__ __forceinline__ void exp_chunk_mixed(const uint32_t (&v)[32], uint32_
         const float2 x1 = __ffma2_rn(
             make_float2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])), scale2, neg2);
         const float2 p0 = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
-        const bool poly = POLY_EVERY > 0 && (i / 4) % (POLY_EVERY > 0 ? POLY_EVERY : 1) == 0;
+        const bool poly = (POLY_MASK >> (i / 4)) & 1;
         const float2 p1 = poly ? exp2_poly2(x1) : make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
         sum0 = __fadd2_rn(sum0, p0);
         sum1 = __fadd2_rn(sum1, p1);
