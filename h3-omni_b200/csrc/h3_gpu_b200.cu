@@ -175,6 +175,7 @@ static void pipeline_release(h3_gpu *g) {
     if (!p.ready) return;
     cudaStreamSynchronize(p.h2d);
     cudaStreamSynchronize(p.d2h);
+    for (cudaStream_t stream : p.compute) cudaStreamSynchronize(stream);
     for (auto &slot : p.slot)
         for (void *&buffer : slot) {
             if (buffer) cudaFree(buffer);
@@ -185,8 +186,10 @@ static void pipeline_release(h3_gpu *g) {
         cudaEventDestroy(p.computed[s]);
         cudaEventDestroy(p.stored[s]);
     }
+    cudaEventDestroy(p.entry);
     cudaStreamDestroy(p.h2d);
     cudaStreamDestroy(p.d2h);
+    for (cudaStream_t stream : p.compute) cudaStreamDestroy(stream);
     p = host_pipeline{};
 }
 extern "C" void h3_gpu_free(h3_gpu *g) {
@@ -423,7 +426,10 @@ static int pipeline_prepare(h3_gpu *g, size_t slot_bytes) {
     if (p.ready && p.slot_bytes >= slot_bytes) return 1;
     pipeline_release(g);
     if (!cuda_good(g, cudaStreamCreateWithFlags(&p.h2d, cudaStreamNonBlocking)) ||
-        !cuda_good(g, cudaStreamCreateWithFlags(&p.d2h, cudaStreamNonBlocking)))
+        !cuda_good(g, cudaStreamCreateWithFlags(&p.d2h, cudaStreamNonBlocking)) ||
+        !cuda_good(g, cudaStreamCreateWithFlags(&p.compute[0], cudaStreamNonBlocking)) ||
+        !cuda_good(g, cudaStreamCreateWithFlags(&p.compute[1], cudaStreamNonBlocking)) ||
+        !cuda_good(g, cudaEventCreateWithFlags(&p.entry, cudaEventDisableTiming)))
         return 0;
     for (int s = 0; s < 2; s++) {
         if (!cuda_good(g, cudaEventCreateWithFlags(&p.loaded[s], cudaEventDisableTiming)) ||
@@ -437,12 +443,13 @@ static int pipeline_prepare(h3_gpu *g, size_t slot_bytes) {
     p.ready = true;
     return 1;
 }
-// How the heads of a host-buffer call are cut into chunks that run back to back. The copy-in
-// before the first kernel and the copy-out after the last one are the only transfers nothing
-// overlaps, so the first and the last chunk are short. head_groups > 0: equal groups, the two
-// outer ones halved. head_groups == 0: the outer chunks are two heads and the inner chunk size is
-// the one that wastes the fewest CTA waves (a chunk of n heads launches n * ceil(sequence / 256)
-// CTAs on `sms` SMs, and its last wave is partly empty), ties going to the smaller chunk.
+// How the heads of a host-buffer call are cut into chunks. The copy-in before the first kernel
+// and the copy-out after the last one are the only transfers nothing overlaps, so the chunks at
+// both ends are short. head_groups > 0: equal groups, the two outer ones halved. head_groups == 0:
+// two one-head chunks at either end and inner chunks of at least two heads and about 24 MB per
+// tensor (large enough for the copy engines; small chunks cost nothing on the compute side
+// because the kernels of consecutive chunks run on two streams and overlap, so no chunk's last,
+// partly empty wave of CTAs leaves SMs idle).
 extern "C" uint32_t h3b_sdpa_host_plan(uint32_t sequence, uint32_t heads, uint32_t head_groups, uint32_t *head_count,
                                        uint32_t capacity) {
     uint32_t chunks = 0;
@@ -464,28 +471,18 @@ extern "C" uint32_t h3b_sdpa_host_plan(uint32_t sequence, uint32_t heads, uint32
             }
         }
     } else {
-        int device = 0, sms = 148;
-        if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-        const uint64_t per_head = (sequence + 255) / 256;
-        auto waves = [&](uint32_t n) { return (n * per_head + sms - 1) / sms; };
         const uint32_t edge = heads >= 8 ? 2 : heads >= 4 ? 1 : 0, inner = heads - 2 * edge;
-        uint32_t best = 1;
-        uint64_t best_waves = ~0ull;
-        for (uint32_t c = 1; c <= 8 && c <= inner; c++) {
-            const uint32_t n = (inner + c - 1) / c, small = n * c - inner;   // `small` chunks hold c - 1 heads
-            if (small > n || (c == 1 && small)) continue;
-            const uint64_t w = (n - small) * waves(c) + small * waves(c - 1);
-            if (w < best_waves) {
-                best_waves = w;
-                best = c;
-            }
-        }
-        push(edge);
+        const uint64_t head_bytes = (uint64_t)sequence * 256;
+        uint32_t best = (uint32_t)((24ull << 20) / head_bytes);
+        best = best < 2 ? 2 : best > 8 ? 8 : best;
+        if (best < (inner + 59) / 60) best = (inner + 59) / 60;   // never more than 64 chunks
+        if (best > inner) best = inner;
+        for (uint32_t i = 0; i < edge; i++) push(1);
         if (inner) {
-            const uint32_t n = (inner + best - 1) / best, small = n * best - inner;
-            for (uint32_t i = 0; i < n; i++) push(i < n - small ? best : best - 1);
+            const uint32_t n = (inner + best - 1) / best, base = inner / n, extra = inner % n;
+            for (uint32_t i = 0; i < n; i++) push(i < extra ? base + 1 : base);
         }
-        push(edge);
+        for (uint32_t i = 0; i < edge; i++) push(1);
     }
     return chunks <= capacity ? chunks : 0;
 }
@@ -517,18 +514,23 @@ extern "C" int h3b_sdpa_bf16_host(h3_gpu *g, uint16_t *out, const uint16_t *q, c
     if (!pipeline_prepare(g, (size_t)widest * 256 * sequence)) return 0;
     host_pipeline &p = g->pipe;
     // everything already queued on the context's stream comes first
-    if (!cuda_good(g, cudaEventRecord(p.computed[0], g->stream)) ||
-        !cuda_good(g, cudaStreamWaitEvent(p.h2d, p.computed[0], 0)))
+    if (!cuda_good(g, cudaEventRecord(p.entry, g->stream)) || !cuda_good(g, cudaStreamWaitEvent(p.h2d, p.entry, 0)) ||
+        !cuda_good(g, cudaStreamWaitEvent(p.compute[0], p.entry, 0)) ||
+        !cuda_good(g, cudaStreamWaitEvent(p.compute[1], p.entry, 0)))
         return 0;
     for (uint32_t chunk = 0; chunk < chunks; chunk++) {
+        // Slot s and stream s belong to the chunks of parity s. The kernels of two consecutive
+        // chunks may overlap: the CTAs of the later one fill the SMs the earlier one's last
+        // wave leaves idle, which is what makes one-head chunks at both ends affordable.
         const int s = chunk & 1;
+        cudaStream_t compute = p.compute[s];
         const uint32_t n = head_count[chunk];
         const size_t offset = (size_t)first_head[chunk] * 128;   // elements into a host row
         const size_t row_bytes = (size_t)n * 256;
         if (chunk >= 2) {
             // slot reuse: inputs after the kernel of chunk-2, output after its copy-out
             if (!cuda_good(g, cudaStreamWaitEvent(p.h2d, p.computed[s], 0)) ||
-                !cuda_good(g, cudaStreamWaitEvent(g->stream, p.stored[s], 0)))
+                !cuda_good(g, cudaStreamWaitEvent(compute, p.stored[s], 0)))
                 return 0;
         }
         const uint16_t *src[3] = {q, k, v};
@@ -537,17 +539,18 @@ extern "C" int h3b_sdpa_bf16_host(h3_gpu *g, uint16_t *out, const uint16_t *q, c
                                               row_bytes, sequence, cudaMemcpyHostToDevice, p.h2d)))
                 return 0;
         if (!cuda_good(g, cudaEventRecord(p.loaded[s], p.h2d)) ||
-            !cuda_good(g, cudaStreamWaitEvent(g->stream, p.loaded[s], 0)) ||
+            !cuda_good(g, cudaStreamWaitEvent(compute, p.loaded[s], 0)) ||
             !cuda_good(g, h3_flash3_bf16(p.slot[s][3], p.slot[s][0], p.slot[s][1], p.slot[s][2], nullptr,
-                                       1, sequence, n, n, scale, g->stream)) ||
-            !cuda_good(g, cudaEventRecord(p.computed[s], g->stream)) ||
+                                       1, sequence, n, n, scale, compute)) ||
+            !cuda_good(g, cudaEventRecord(p.computed[s], compute)) ||
             !cuda_good(g, cudaStreamWaitEvent(p.d2h, p.computed[s], 0)) ||
             !cuda_good(g, cudaMemcpy2DAsync(out + offset, pitch, p.slot[s][3], row_bytes, row_bytes,
                                           sequence, cudaMemcpyDeviceToHost, p.d2h)) ||
             !cuda_good(g, cudaEventRecord(p.stored[s], p.d2h)))
             return 0;
     }
-    return cuda_good(g, cudaStreamSynchronize(p.d2h)) && cuda_good(g, cudaStreamSynchronize(g->stream));
+    return cuda_good(g, cudaStreamSynchronize(p.d2h)) && cuda_good(g, cudaStreamSynchronize(p.compute[0])) &&
+           cuda_good(g, cudaStreamSynchronize(p.compute[1])) && cuda_good(g, cudaStreamSynchronize(g->stream));
 }
 
 // ======================= Q/K norm + rotary embedding (attention's producer) =======================

@@ -13,8 +13,8 @@
 struct host_pipeline {
     void *slot[2][4]{};            // q, k, v, out per slot
     size_t slot_bytes{};
-    cudaStream_t h2d{}, d2h{};
-    cudaEvent_t loaded[2]{}, computed[2]{}, stored[2]{};
+    cudaStream_t h2d{}, d2h{}, compute[2]{};   // kernels of consecutive chunks alternate between two streams
+    cudaEvent_t loaded[2]{}, computed[2]{}, stored[2]{}, entry{};
     bool ready{};
 };
 struct h3_gpu {

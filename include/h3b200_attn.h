@@ -259,9 +259,10 @@ int h3b_attention_output_gate_adaln_bf16(
  * chunks, and copy-in, kernel and copy-out of consecutive chunks overlap on three streams, so the
  * call costs about max(copy time, kernel time). head_groups > 0: that many equal groups
  * (heads % head_groups == 0, at most 64), the first and the last run as two halves to shorten the
- * two transfers nothing can overlap. head_groups == 0: the library chooses - outer chunks of two
- * heads, inner chunks of the size whose kernel launches waste the fewest CTA waves on this GPU
- * (24 heads of 52,352 rows on 148 SMs: 2 5 5 5 5 2). Synchronous: returns when `out` is complete.
+ * two transfers nothing can overlap. head_groups == 0: the library chooses - two one-head chunks
+ * at either end, inner chunks of at least two heads and about 24 MB per tensor (24 heads of 52,352
+ * rows: 1 1 2 2 2 2 2 2 2 2 2 2 1 1). The kernels of consecutive chunks run on two streams and
+ * overlap, so short chunks leave no SM idle. Synchronous: returns when `out` is complete.
  * h3b_sdpa_host_plan returns the number of chunks such a call uses and writes their head counts
  * (0: the heads do not split that way, or more than `capacity` chunks). */
 uint32_t h3b_sdpa_host_plan(uint32_t sequence, uint32_t heads, uint32_t head_groups, uint32_t *head_count,

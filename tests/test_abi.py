@@ -58,9 +58,9 @@ def test_calls_without_a_context_fail_cleanly(library):
 
 
 def test_host_call_plans_its_head_chunks(library):
-    """h3b_sdpa_host_plan is host arithmetic (no GPU: it assumes 148 SMs when no device answers):
-    equal groups with the outer two halved, or, asked to choose, outer chunks of two heads and the
-    inner chunk size that wastes the fewest CTA waves - five heads of 205 CTAs fill 6.93 waves."""
+    """h3b_sdpa_host_plan is host arithmetic: equal groups with the outer two halved, or, asked
+    to choose, two one-head chunks at either end and inner chunks of at least two heads and
+    about 24 MB per tensor."""
     _, lib = library
     lib.h3b_sdpa_host_plan.restype = C.c_uint32
     counts = (C.c_uint32 * 66)()
@@ -69,7 +69,9 @@ def test_host_call_plans_its_head_chunks(library):
         return list(counts[:lib.h3b_sdpa_host_plan(sequence, heads, groups, counts, capacity)])
 
     assert plan(52352, 24, 6) == [2, 2, 4, 4, 4, 4, 2, 2]
-    assert plan(52352, 24, 0) == [2, 5, 5, 5, 5, 2]
+    assert plan(52352, 24, 0) == [1, 1] + [2] * 10 + [1, 1]
+    assert plan(16384, 24, 0) == [1, 1, 5, 5, 5, 5, 1, 1] and plan(16384, 11, 0) == [1, 1, 4, 3, 1, 1]
+    assert len(plan(101464, 200, 0)) <= 64
     assert plan(700, 8, 1) == [4, 4] and plan(700, 8, 4) == [1, 1, 2, 2, 1, 1]
     assert plan(700, 8, 3) == [] and plan(700, 0, 0) == [] and plan(52352, 24, 6, capacity=4) == []
     for heads in range(1, 65):
