@@ -87,7 +87,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                      const PairParams p) {
     constexpr int ST = PAIR_STAGES;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t bars[1 + 2 * ST + 7];
+    __shared__ uint64_t bars[1 + 2 * ST + 9];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_word;
     __shared__ int skip_launch;
@@ -105,8 +105,8 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     auto bar_s_full = [&](int t) { return bar0 + 8u * (1 + 2 * ST + t); };
     // P is handed over in two halves of 64 keys so that the first four PV MMAs run while the
     // exponentials of the second half are still being taken
-    auto bar_p_full = [&](int t, int half) { return bar0 + 8u * (1 + 2 * ST + 2 + 2 * t + half); };
-    const uint32_t bar_pv_done = bar0 + 8u * (1 + 2 * ST + 6);   // the last PV of both tiles
+    auto bar_p_full = [&](int t, int piece) { return bar0 + 8u * (1 + 2 * ST + 2 + 3 * t + piece); };
+    const uint32_t bar_pv_done = bar0 + 8u * (1 + 2 * ST + 8);   // the last PV of both tiles
 
     const int head = blockIdx.y, batch = p.split_tiles ? 0 : blockIdx.z, out_batch = blockIdx.z;
     const int kv_head = head / (p.heads / p.kv_heads);
@@ -127,8 +127,10 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         for (int t = 0; t < 2; t++) mbar_init(bar_s_full(t), 1);
         mbar_init(bar_p_full(0, 0), 128 + 1);   // the softmax threads of tile A and the ring watcher
         mbar_init(bar_p_full(0, 1), 128);
+        mbar_init(bar_p_full(0, 2), 128);
         mbar_init(bar_p_full(1, 0), 128);
         mbar_init(bar_p_full(1, 1), 128);
+        mbar_init(bar_p_full(1, 2), 128);
         mbar_init(bar_pv_done, 1);
         mbar_fence_init();
         abort_word = 0;
@@ -214,15 +216,15 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
                 __syncwarp();
             };
-            auto issue_pv = [&](int j, int t, int half) {   // O_t += P_t . V_j over 64 of the 128 keys
+            auto issue_pv = [&](int j, int t, int piece) {   // O_t += P_t . V_j over keys 0-63, 64-95 or 96-127
                 const uint32_t v_lo = v_ring_lo + ((2 * j + 1) % ST) * (PAIR_TILE_BYTES >> 4);
+                const int first = piece == 0 ? 0 : piece == 1 ? 4 : 6, last = piece == 0 ? 4 : piece == 1 ? 6 : 8;
                 if (leader) {
 #pragma unroll
-                    for (int k4 = 0; k4 < PBN / 32; k4++) {
-                        const int kk = half * (PBN / 32) + k4;
-                        mma_ts_words(tmem + PAIR_O_COL + t * PHD, tmem + t * PBN + kk * 8,
-                                     v_lo + kk * (2048 >> 4), v_hi, idesc_pv, (j > 0) || (kk > 0));
-                    }
+                    for (int kk = 0; kk < 8; kk++)
+                        if (kk >= first && kk < last)
+                            mma_ts_words(tmem + PAIR_O_COL + t * PHD, tmem + t * PBN + kk * 8,
+                                         v_lo + kk * (2048 >> 4), v_hi, idesc_pv, (j > 0) || (kk > 0));
                 }
                 __syncwarp();
             };
@@ -256,6 +258,9 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     if (!mbar_wait_converged(bar_p_full(0, 1), j & 1, &abort_word)) break;
                     tc5_fence_after();
                     issue_pv(j, 0, 1);
+                    if (!mbar_wait_converged(bar_p_full(0, 2), j & 1, &abort_word)) break;
+                    tc5_fence_after();
+                    issue_pv(j, 0, 2);
                     TRACE_ADD(4);
                 }
                 if (more) {
@@ -275,6 +280,9 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     if (!mbar_wait_converged(bar_p_full(1, 1), j & 1, &abort_word)) break;
                     tc5_fence_after();
                     issue_pv(j, 1, 1);
+                    if (!mbar_wait_converged(bar_p_full(1, 2), j & 1, &abort_word)) break;
+                    tc5_fence_after();
+                    issue_pv(j, 1, 2);
                     release(2 * j + 1);
                     TRACE_ADD(6);
                 }
@@ -349,7 +357,7 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #ifdef H3B_TRACE
             const long long trace_work = clock64();
 #endif
-            bool first_half_out = false;
+            bool first_half_out = false, second_piece_out = false;
             if (nvalid >= PBN) {
                 // the whole row of scores in registers: one TMEM read pass
                 uint32_t s0[32], s1[32], s2[32], s3[32];
@@ -398,6 +406,10 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 first_half_out = true;
                 exp_chunk_mixed<PAIR_POLY_EVERY>(s2, packed, scale2, neg2, sum0, sum1);
                 tmem_st16(s_addr + 32, packed);
+                tmem_wait_st();
+                tc5_fence_before();
+                mbar_arrive(bar_p_full(t, 1));
+                second_piece_out = true;
                 exp_chunk_mixed<PAIR_POLY_EVERY>(s3, packed, scale2, neg2, sum0, sum1);
                 tmem_st16(s_addr + 48, packed);
                 l += (sum0.x + sum0.y) + (sum1.x + sum1.y);
@@ -429,7 +441,8 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             tmem_wait_st();
             tc5_fence_before();
             if (!first_half_out) mbar_arrive(bar_p_full(t, 0));
-            mbar_arrive(bar_p_full(t, 1));
+            if (!second_piece_out) mbar_arrive(bar_p_full(t, 1));
+            mbar_arrive(bar_p_full(t, 2));
 #ifdef H3B_TRACE
             g_pair_trace_local[1] += clock64() - trace_work;
 #endif
