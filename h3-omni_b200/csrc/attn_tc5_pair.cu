@@ -22,8 +22,8 @@
 // S(j) also covers PV(j-1), issued before it by the same thread. The ring has five slots: a tile
 // takes 2000-3000 cycles from the request to shared memory when every SM asks at once, and with
 // four slots (two steps of K/V) the request for step j+2 cannot leave before step j is over.
-// P goes to the issuer in two halves of 64 keys, so the first four PV MMAs of a tile run while the
-// second half of its exponentials is still being taken; waits that are expected to be long park
+// P goes to the issuer in three pieces (keys 0-63, 64-95, 96-127), so six of a tile's eight PV
+// MMAs run while the rest of its exponentials is still being taken; waits that are expected to be long park
 // in hardware (mbar_wait_parked) - at the board's power limit a spinning warp costs clock.
 // A fixed fraction of the exponentials is evaluated by a polynomial on the FMA pipe (see
 // softmax_tc5.cuh) so the exponential unit is not the critical resource.
@@ -103,8 +103,8 @@ attn_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     auto bar_full = [&](int s) { return bar0 + 8u * (1 + s); };
     auto bar_empty = [&](int s) { return bar0 + 8u * (1 + ST + s); };
     auto bar_s_full = [&](int t) { return bar0 + 8u * (1 + 2 * ST + t); };
-    // P is handed over in two halves of 64 keys so that the first four PV MMAs run while the
-    // exponentials of the second half are still being taken
+    // P is handed over in three pieces (keys 0-63, 64-95, 96-127) so that PV MMAs run while the
+    // later exponentials are still being taken
     auto bar_p_full = [&](int t, int piece) { return bar0 + 8u * (1 + 2 * ST + 2 + 3 * t + piece); };
     const uint32_t bar_pv_done = bar0 + 8u * (1 + 2 * ST + 8);   // the last PV of both tiles
 
